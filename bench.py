@@ -1,0 +1,380 @@
+#!/usr/bin/env python
+"""Headline benchmark: train tokens/s per optimiser step of the SeeML update-plan VM
+on B200 (forward + autodiff backward + AdamW over a frozen base with LoRA adapters).
+
+    python bench.py --gpus 1 --steps K --warmup W
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference ...      # the reference's CPU runtime, same metric
+
+A "step" is one optimiser step over the global batch (config c4: 256 sequences x 512
+tokens = 131072 tokens, executed as 8 chunks of the plan's compiled batch of 16384 rows,
+chunks sharded across the ranks). Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from see_ml_b200 import formats as F  # noqa: E402
+from see_ml_b200 import plansynth as PS  # noqa: E402
+
+# name -> model geometry + LoRA/optimiser request of the benchmark configurations
+CONFIGS = {
+    "c1": dict(kind="mlp", dims=[256, 512, 512, 10], acts=["relu", "gelu", None], rows=32, chunks=1,
+               rank=8, alpha=16.0, targets=(), lr=1e-3),
+    "c2": dict(kind="gpt", vocab=512, d=128, heads=4, ffn=512, layers=2, seq=64, seqs=16, chunks=1,
+               rank=8, alpha=16.0, targets=("wq", "wv"), lr=1e-3),
+    "c3": dict(kind="llama", vocab=4096, d=256, heads=4, ffn=768, layers=4, seq=128, seqs=64, chunks=1,
+               rank=16, alpha=32.0, targets=("wq", "wk", "wv", "wo"), lr=5e-4),
+    "c4": dict(kind="llama", vocab=32000, d=1024, heads=16, ffn=2816, layers=12, seq=512, seqs=32,
+               chunks=8, rank=16, alpha=32.0, targets=("wq", "wk", "wv", "wo", "w_up", "w_down"), lr=3e-4),
+}
+
+
+def build_model(cfg, seed=1):
+    rng = np.random.default_rng(seed)
+    if cfg["kind"] == "mlp":
+        return PS.mlp_model(cfg["dims"], cfg["acts"], rng)
+    fn = PS.llama_decoder if cfg["kind"] == "llama" else PS.gpt_decoder
+    return fn(cfg["vocab"], cfg["d"], cfg["heads"], cfg["ffn"], cfg["layers"], cfg["seq"], rng)
+
+
+def build_plan(cfg, model, rows, hasher):
+    spec = PS.TrainSpec(batch=rows, lora_rank=cfg["rank"], lora_alpha=cfg["alpha"], targets=cfg["targets"],
+                        lr=cfg["lr"], default_steps=1000)
+    return PS.synthesize(model, spec, hasher=hasher)
+
+
+def synth_batches(cfg, rows, n_chunks, seed):
+    """Seeded synthetic corpus of the configuration's shape and value distribution:
+    Zipf(1.1) token ids with next-token labels, or N(0,1) features with uniform labels."""
+    rng = np.random.default_rng(seed)
+    if cfg["kind"] == "mlp":
+        x = rng.standard_normal((n_chunks, rows, cfg["dims"][0])).astype(np.float32)
+        y = rng.integers(0, cfg["dims"][-1], (n_chunks, rows)).astype(np.int32)
+        return x.reshape(n_chunks, -1), y
+    S = cfg["seq"]
+    if cfg["kind"] == "llama":
+        recs = PS.zipf_tokens(rng, cfg["vocab"], (n_chunks, rows // S, S + 1))
+    else:
+        recs = rng.integers(0, cfg["vocab"], (n_chunks, rows // S, S + 1)).astype(np.int32)
+    return (np.ascontiguousarray(recs[:, :, :-1]).reshape(n_chunks, -1),
+            np.ascontiguousarray(recs[:, :, 1:]).reshape(n_chunks, -1))
+
+
+def plan_work(plan_bytes):
+    """Algorithmic GEMM FLOPs (2*M*N*K) of one execution of the train stream, and the
+    largest GEMM instruction by FLOPs."""
+    p = F.parse_plan(plan_bytes)
+    total, top = 0, None
+    for ins in p.train:
+        if int(ins["opcode"]) in (1, 2, 3, 4):
+            m, n, k = (int(v) for v in ins["out"])
+            fl = 2 * m * n * k
+            total += fl
+            if top is None or fl > top[0]:
+                top = (fl, ins.copy())
+    return total, top
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.idx = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.idx), "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                pass
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                   r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+# ------------------------------------------------------------------------------- reference arm
+def cpu_reference_sample(cfg, model, steps, warmup, threads):
+    """Times the reference's own CPU runtime (oracle/_ref) — or the C restatement when the
+    reference build is absent — on a bounded sample of the workload: one sequence (token
+    configs) or one compiled batch (MLP) per step."""
+    from oracle import pyoracle as O
+    rows = cfg["seq"] if cfg["kind"] != "mlp" else cfg["rows"]
+    hasher = lambda b, o: int(O.port().orc_plan_self_hash(np.frombuffer(b, np.uint8).ctypes.data, len(b), o))
+    blob, _ = build_plan(cfg, model, rows, hasher)
+    inp, lab = synth_batches(cfg, rows, 1, seed=5)
+    h = F.PlanHeader.unpack(blob)
+    times = []
+    if O.have_ref():
+        kind = "reference"
+        O.ref().ref_set_threads(threads)
+        e = O.RefEngine(blob)
+        arena = e.arena()
+        arena[h.input_ref:h.input_ref + inp[0].nbytes] = inp[0].view(np.uint8)
+        arena[h.label_ref:h.label_ref + lab[0].nbytes] = lab[0].view(np.uint8)
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            e.execute_train_once()
+            times.append(time.perf_counter() - t0)
+    else:
+        kind, threads = "port", 1
+        plan = F.parse_plan(blob)
+        arena = np.zeros(F.align_up(h.arena_size), np.uint8)
+        arena[:h.persist_init_size] = plan.persist_init
+        arena[h.input_ref:h.input_ref + inp[0].nbytes] = inp[0].view(np.uint8)
+        arena[h.label_ref:h.label_ref + lab[0].nbytes] = lab[0].view(np.uint8)
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            O.execute("port", plan.train, arena, np.asarray(plan.rodata), lr=h.lr, step=i + 1)
+            times.append(time.perf_counter() - t0)
+    t = float(np.mean(times[warmup:])) if steps else float("nan")
+    return dict(value=rows / t, unit="tokens/s", cores=threads, kind=kind,
+                sample=f"{steps} step(s) of {rows} rows (one sequence of the workload's model), "
+                       f"{warmup} warm-up"), t * 1e3
+
+
+def run_reference(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    model = build_model(cfg)
+    threads = os.cpu_count() or 1
+    base, ms = cpu_reference_sample(cfg, model, args.steps, min(args.warmup, 1), threads)
+    line = {"metric": "train tokens/sec per update step", "value": base["value"], "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "impl": "reference", "config": workload_config(args, cfg),
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, cfg):
+    rows = cfg["rows"] if cfg["kind"] == "mlp" else cfg["seqs"] * cfg["seq"]
+    d = {"workload": args.config, "rows_per_chunk": rows, "chunks_per_step": cfg["chunks"],
+         "global_rows_per_step": rows * cfg["chunks"], "lora_rank": cfg["rank"],
+         "lora_targets": list(cfg["targets"]) or "all", "optimizer": "adamw",
+         "l2": "inputs and activations exceed L2 (arena >> 126 MB)" if args.config in ("c3", "c4")
+               else "L2 flushed between timed steps"}
+    for k in ("vocab", "d", "heads", "ffn", "layers", "seq", "dims"):
+        if k in cfg:
+            d[k] = cfg[k]
+    return d
+
+
+# ------------------------------------------------------------------------------------ our arm
+def run_ours(args, cfg):
+    import torch
+    import torch.distributed as dist
+    from see_ml_b200 import _lib as L
+    from see_ml_b200.dp import DataParallelTrainer
+    from see_ml_b200.engine import Context
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the backend has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+        group = dist.group.WORLD
+    lib = L.lib()
+    hasher = lambda b, o: int(lib.seeml_b200_plan_self_hash(np.frombuffer(b, np.uint8).ctypes.data, len(b), o))
+    model = build_model(cfg)
+    rows = cfg["rows"] if cfg["kind"] == "mlp" else cfg["seqs"] * cfg["seq"]
+    K = max(cfg["chunks"], world)
+    blob, _ = build_plan(cfg, model, rows, hasher)
+    gemm = {"tf32x3": 0, "bf16": 1, "simt": 2, "tf32": 3}[args.gemm]
+    tr = DataParallelTrainer(blob, K, rank, world, local_rank, mode=1 if args.fused else 0, gemm=gemm,
+                             group=group)
+    local = tr.local
+    n_steps = args.warmup + args.steps
+    dev = torch.device("cuda", local_rank)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
+
+    def batches_for(step):   # this rank's chunks of the global step (seeded per step)
+        tok, lab = synth_batches(cfg, rows, K, seed=1000 + step)
+        return tok[rank * local:(rank + 1) * local], lab[rank * local:(rank + 1) * local]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- arm A: inputs resident in HBM ----------------------------------------------------
+    host = [batches_for(s) for s in range(min(n_steps, 4))]
+    resident = [(torch.from_numpy(np.ascontiguousarray(t)).to(dev), torch.from_numpy(np.ascontiguousarray(l)).to(dev))
+                for t, l in host]
+    for s in range(args.warmup):
+        tr.step_resident(*resident[s % len(resident)])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = 0
+    with torch.cuda.stream(tr.stream):
+        ev0.record()
+        for s in range(args.steps):
+            if args.config in ("c1", "c2"):
+                flush.fill_(s & 1)
+            tr.step_resident(*resident[(args.warmup + s) % len(resident)])
+            launches += tr.launches
+        ev1.record()
+    barrier()
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    clocks = sampler.stop() if rank == 0 else None
+    loss_a = tr.engine.loss_value()
+    ms_step = ms_total / args.steps
+    tokens = rows * K
+    value = tokens / (ms_step * 1e-3)
+
+    # ---- arm B: end to end through the public API from host buffers --------------------------
+    e2e_steps = max(1, min(args.steps, 3))
+    hb = [batches_for(100 + s) for s in range(e2e_steps + 1)]
+    tr.step(*hb[0])
+    barrier()
+    with torch.cuda.stream(tr.stream):
+        ev0.record()
+        for s in range(e2e_steps):
+            loss_b = tr.step(*hb[1 + s])
+        ev1.record()
+    barrier()
+    e2e_ms = max_over_ranks(ev0.elapsed_time(ev1)) / e2e_steps
+    e2e = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
+           "h2d_bytes_per_step": int(tr.h2d_bytes * world), "d2h_bytes_per_step": int(tr.d2h_bytes * world),
+           "ms_per_step": e2e_ms, "steps": e2e_steps}
+
+    if rank == 0:
+        hbm, tf_burst, tf_sust, src = measured_peaks()
+        flops, top = plan_work(blob)
+        # roofline of the dominant kernel: the largest GEMM instruction of the stream, timed
+        # alone with CUDA events on the stream it is launched on
+        roof = None
+        if top is not None:
+            fl, ins = top
+            m, n, k = (int(v) for v in ins["out"])
+            ctx = Context((m * k + k * n + m * n) * 4 + 4096, None, device=local_rank, gemm=gemm)
+            gi = np.zeros(1, dtype=F.INSTR_DTYPE)
+            gi["in"] = F.NULL_REF
+            gi["opcode"] = 2    # A[M,K] @ B[N,K]^T: both operands K-major, the tensor-core form
+            a_off, b_off = 0, F.align_up(m * k * 4)
+            c_off = b_off + F.align_up(k * n * 4)
+            gi["in"][0, :3] = (a_off, b_off, c_off)
+            gi["out"][0] = (m, n, k)
+            rng = np.random.default_rng(0)
+            ctx.write(a_off, rng.standard_normal(m * k, dtype=np.float32))
+            ctx.write(b_off, rng.standard_normal(k * n, dtype=np.float32))
+            pid = ctx.build(gi)
+            st = torch.cuda.ExternalStream(lib.seeml_b200_ctx_stream(ctx.h), device=dev)
+            for _ in range(3):
+                ctx.run(pid, 0, 1)
+            reps = 10
+            with torch.cuda.stream(st):
+                ev0.record()
+                for _ in range(reps):
+                    ctx.run(pid, 0, 1, sync=False)
+                ev1.record()
+            torch.cuda.synchronize()
+            t_ms = ev0.elapsed_time(ev1) / reps
+            ach = fl / (t_ms * 1e-3) / 1e12
+            roof = {"bound": "tensor", "kernel": f"gemm M={m} N={n} K={k} ({args.gemm})",
+                    "achieved": ach, "peak": tf_burst, "unit": "TFLOP/s", "frac": ach / tf_burst,
+                    "peak_source": f"bf16 dense burst, {src}", "traffic": None, "ms_per_launch": t_ms}
+            ctx.close()
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            cpu, _ = cpu_reference_sample(cfg, model, 1, 0, os.cpu_count() or 1)
+        line = {"metric": "train tokens/sec per update step", "value": value, "unit": "tokens/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": {"tf32x3": "f32 (3xTF32 tensor-core split, f32 accumulate)", "bf16": "bf16",
+                          "simt": "f32", "tf32": "tf32"}[args.gemm],
+                "data": "synthetic", "config": workload_config(args, cfg),
+                "mode": "fused" if args.fused else "contract",
+                "gemm_tflops_algorithmic": flops * K / (ms_step * 1e-3) / 1e12,
+                "loss": loss_a, "e2e": e2e, "gpu_launches": int(launches),
+                "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
+        print(json.dumps(line), flush=True)
+    tr.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c4", choices=sorted(CONFIGS))
+    ap.add_argument("--gemm", default="tf32x3", choices=["tf32x3", "bf16", "simt", "tf32"])
+    ap.add_argument("--fused", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,82 @@
+// Device context and program executor behind the C ABI (include/seeml_b200.h).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "kernels.h"
+#include "plan_abi.h"
+#include "seeml_b200.h"
+
+namespace seeml_b200 {
+
+void set_error(const std::string& msg);
+int fail(const std::string& msg);           // sets the message, returns 1
+int cuda_fail(cudaError_t e, const char* what);
+
+// Host-side validator (validate.cc): empty string = accepted.
+std::string validate_instruction(const Instr& ins, uint64_t arena_size, uint64_t rodata_size,
+                                 uint32_t version);
+std::string verify_plan(const uint8_t* plan, uint64_t size, PlanHeader* header_out);
+uint64_t content_hash64(const uint8_t* p, uint64_t n);
+uint64_t plan_self_hash(const uint8_t* p, uint64_t n, uint64_t hash_off);
+
+// Tensor-core GEMM hooks (gemm_tc.cu). gemm_tensor_core returns 1 when it handled
+// the instruction (launch count in *launches), 0 when the shape/operands are not
+// eligible (the CUDA-core path runs instead), -1 on error.
+}  // namespace seeml_b200
+struct seeml_b200_ctx;
+namespace seeml_b200 {
+int gemm_tensor_core(seeml_b200_ctx* c, const Instr& ins, int* launches);
+int gemm_tensor_core_prepare(seeml_b200_ctx* c, const Instr& ins);
+void gemm_tensor_core_release(seeml_b200_ctx* c);
+
+struct Program {
+  std::vector<Instr> instrs;
+  uint32_t version = kSeeuVersion;
+  uint32_t mode = SEEML_B200_MODE_CONTRACT;
+  uint64_t last_launches = 0;
+  // captured graphs per executed range
+  std::map<std::pair<uint64_t, uint64_t>, cudaGraphExec_t> graphs;
+};
+
+}  // namespace seeml_b200
+
+struct seeml_b200_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr, copy_stream = nullptr;
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  // device staging double buffer for batches (feeder): H2D on copy_stream, D2D on stream
+  struct Stage {
+    uint8_t* dev = nullptr;
+    uint64_t cap = 0, input_bytes = 0, label_bytes = 0;
+    cudaEvent_t h2d_done = nullptr, consumed = nullptr;
+    bool pending_consume = false;
+  } stage[2];
+  uint8_t* arena = nullptr;
+  uint64_t arena_bytes = 0;
+  bool owns_arena = true;
+  uint8_t* rodata = nullptr;
+  uint64_t rodata_bytes = 0;
+  uint32_t gemm_kind = SEEML_B200_GEMM_TF32X3;
+  bool timing = false, timed_valid = false;
+  bool use_graphs = false;
+  seeml_b200::DevScalars* scalars_dev = nullptr;
+  double* loss_scratch = nullptr;
+  uint64_t loss_scratch_doubles = 0;
+  float* gemm_ws = nullptr;
+  uint64_t gemm_ws_floats = 0;
+  float* read_slot = nullptr;  // pinned
+  // transposed copies of frozen weights, keyed by (rodata offset, rows K, cols N): [N][K]
+  std::map<std::tuple<uint64_t, uint64_t, uint64_t>, float*> wt;
+  // RoPE (cos,sin) tables keyed by (S, d, base bits)
+  std::map<std::tuple<uint64_t, uint64_t, uint32_t>, float2*> rope;
+  seeml_b200::k::Span* spans_dev = nullptr;
+  uint64_t spans_cap = 0;
+  std::vector<std::unique_ptr<seeml_b200::Program>> programs;
+};

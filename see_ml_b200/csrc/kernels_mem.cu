@@ -1,0 +1,936 @@
+// Memory-bound kernels of the update ISA for sm_100a: elementwise / broadcast,
+// activations, LayerNorm / RMSNorm, RoPE, row softmaxes, losses, the optimiser
+// family and the gradient pack / tree-sum helpers. Built with -fmad=false so the
+// per-element expressions round exactly like the reference's scalar C++ (which is
+// compiled without FMA contraction); reductions the reference carries in double
+// are carried in double here, in a fixed lane/warp order, so a run is
+// bit-reproducible. All kernels are HBM-bound: 128-bit accesses where the
+// operands allow, grids sized in multiples of the 148 SMs.
+#include <cmath>
+
+#include "kernels.h"
+
+namespace seeml_b200 {
+namespace k {
+namespace {
+
+constexpr int kSMs = 148;
+constexpr int kThreads = 256;
+
+inline int grid_for(size_t work_items, int per_block, int waves = 8) {
+  size_t blocks = (work_items + per_block - 1) / per_block;
+  size_t cap = static_cast<size_t>(kSMs) * waves;
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  return static_cast<int>(blocks);
+}
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- activation expressions (kernel_policy.h:53-67, activation.cc:40-75) --------
+__device__ __forceinline__ float sigmoid_e(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float relu_e(float x) { return x > 0.0f ? x : 0.0f; }
+__device__ __forceinline__ float gelu_e(float x) {
+  const float t = tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x));
+  return 0.5f * x * (1.0f + t);
+}
+__device__ __forceinline__ float silu_e(float x) { return x * sigmoid_e(x); }
+__device__ __forceinline__ float gelu_d(float dy, float v) {
+  const float kC = 0.7978845608028654f, kA = 0.044715f;
+  const float u = kC * (v + kA * v * v * v);
+  const float t = tanhf(u);
+  const float sech2 = 1.0f - t * t;
+  const float tail = sech2 == 0.0f ? 0.0f : 0.5f * v * sech2 * (kC * (1.0f + 3.0f * kA * v * v));
+  return dy * (0.5f * (1.0f + t) + tail);
+}
+__device__ __forceinline__ float silu_d(float dy, float x) {
+  const float s = sigmoid_e(x);
+  return dy * (s * (1.0f + x * (1.0f - s)));
+}
+__device__ __forceinline__ float act_apply(int act, float v) {
+  return act == 1 ? relu_e(v) : act == 2 ? gelu_e(v) : act == 3 ? silu_e(v) : v;
+}
+
+// ---- generic elementwise: out[i] = f(a[i], b[i]) ---------------------------------
+struct FAdd { __device__ float operator()(float a, float b) const { return a + b; } };
+struct FMul { __device__ float operator()(float a, float b) const { return a * b; } };
+struct FScale { float alpha; __device__ float operator()(float a, float) const { return alpha * a; } };
+struct FFill { float v; __device__ float operator()(float, float) const { return v; } };
+struct FAct { int act; __device__ float operator()(float a, float) const { return act_apply(act, a); } };
+struct FActBwd {
+  int act;
+  __device__ float operator()(float dy, float x) const {
+    return act == 1 ? (x > 0.0f ? dy : 0.0f) : act == 2 ? gelu_d(dy, x) : silu_d(dy, x);
+  }
+};
+
+template <int NIN, class F>
+__global__ void __launch_bounds__(kThreads) ew_vec(F f, const float4* __restrict__ a,
+                                                   const float4* __restrict__ b,
+                                                   float4* __restrict__ o, size_t n4) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4;
+       i += (size_t)gridDim.x * blockDim.x) {
+    float4 x = NIN >= 1 ? a[i] : make_float4(0, 0, 0, 0);
+    float4 y = NIN >= 2 ? b[i] : make_float4(0, 0, 0, 0);
+    float4 r;
+    r.x = f(x.x, y.x); r.y = f(x.y, y.y); r.z = f(x.z, y.z); r.w = f(x.w, y.w);
+    o[i] = r;
+  }
+}
+template <int NIN, class F>
+__global__ void __launch_bounds__(kThreads) ew_scalar(F f, const float* __restrict__ a,
+                                                      const float* __restrict__ b,
+                                                      float* __restrict__ o, size_t begin, size_t n) {
+  for (size_t i = begin + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    o[i] = f(NIN >= 1 ? a[i] : 0.0f, NIN >= 2 ? b[i] : 0.0f);
+}
+template <int NIN, class F>
+int launch_ew(F f, const float* a, const float* b, float* o, size_t n, cudaStream_t st) {
+  if (n == 0) return 0;
+  int launches = 0;
+  const bool vec = aligned16(o) && (NIN < 1 || aligned16(a)) && (NIN < 2 || aligned16(b));
+  size_t done = 0;
+  if (vec && n >= 4) {
+    const size_t n4 = n / 4;
+    ew_vec<NIN, F><<<grid_for(n4, kThreads), kThreads, 0, st>>>(
+        f, reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b),
+        reinterpret_cast<float4*>(o), n4);
+    done = n4 * 4;
+    ++launches;
+  }
+  if (done < n) {
+    ew_scalar<NIN, F><<<grid_for(n - done, kThreads), kThreads, 0, st>>>(f, a, b, o, done, n);
+    ++launches;
+  }
+  return launches;
+}
+
+// ---- broadcast over columns: out[r,c] = act(x[r,c] + b[c]) -------------------------
+__global__ void __launch_bounds__(kThreads) bias_act_kernel(const float* __restrict__ x,
+                                                            const float* __restrict__ bias,
+                                                            float* __restrict__ o, size_t rows,
+                                                            size_t cols, int act) {
+  const size_t n = rows * cols;
+  if ((cols & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(o) |
+                           reinterpret_cast<uintptr_t>(bias)) & 15u) == 0) {
+    const size_t n4 = n >> 2, c4 = cols >> 2;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4;
+         i += (size_t)gridDim.x * blockDim.x) {
+      float4 v = reinterpret_cast<const float4*>(x)[i];
+      if (bias) {
+        const float4 bb = reinterpret_cast<const float4*>(bias)[i % c4];
+        v.x = v.x + bb.x; v.y = v.y + bb.y; v.z = v.z + bb.z; v.w = v.w + bb.w;
+      }
+      v.x = act_apply(act, v.x); v.y = act_apply(act, v.y);
+      v.z = act_apply(act, v.z); v.w = act_apply(act, v.w);
+      reinterpret_cast<float4*>(o)[i] = v;
+    }
+  } else {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+      float v = x[i];
+      if (bias) v = v + bias[i % cols];
+      o[i] = act_apply(act, v);
+    }
+  }
+}
+
+// ---- embedding gather: one warp per row, 128-bit copies -------------------------------
+__global__ void __launch_bounds__(kThreads) embed_kernel(const int32_t* __restrict__ tok,
+                                                         const float* __restrict__ table,
+                                                         float* __restrict__ o, size_t rows,
+                                                         size_t dim, int vec) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t r = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const float* src = table + (size_t)tok[r] * dim;
+    float* dst = o + r * dim;
+    if (vec) {
+      for (size_t c = lane; c < (dim >> 2); c += 32)
+        reinterpret_cast<float4*>(dst)[c] = reinterpret_cast<const float4*>(src)[c];
+    } else {
+      for (size_t c = lane; c < dim; c += 32) dst[c] = src[c];
+    }
+  }
+}
+
+// db[c] = sum_r dy[r,c], rows ascending (elementwise.cc:55-67): one thread per column.
+__global__ void reduce_rows_kernel(const float* __restrict__ dy, float* __restrict__ db,
+                                   size_t rows, size_t cols) {
+  const size_t c = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float acc = 0.0f;
+  for (size_t r = 0; r < rows; ++r) acc += dy[r * cols + c];
+  db[c] = acc;
+}
+
+// ---- row reductions in a fixed order ---------------------------------------------------
+// TPR threads cooperate on one row (32 = one warp, 256 = one block).
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int TPR>
+__device__ __forceinline__ double row_sum(double v, double* sm) {
+  v = warp_sum(v);
+  if (TPR == 32) return v;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) sm[w] = v;
+  __syncthreads();
+  double t = 0.0;
+#pragma unroll
+  for (int i = 0; i < TPR / 32; ++i) t += sm[i];
+  return t;
+}
+template <int TPR>
+__device__ __forceinline__ float row_max(float v, float* sm) {
+  v = warp_max(v);
+  if (TPR == 32) return v;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) sm[w] = v;
+  __syncthreads();
+  float t = sm[0];
+#pragma unroll
+  for (int i = 1; i < TPR / 32; ++i) t = fmaxf(t, sm[i]);
+  return t;
+}
+#define ROW_SETUP(TPR)                                                         \
+  __shared__ double smd[8];                                                    \
+  const int lane = TPR == 32 ? (threadIdx.x & 31) : threadIdx.x;               \
+  const size_t rpb = kThreads / TPR;                                           \
+  const size_t row0 = blockIdx.x * rpb + (TPR == 32 ? (threadIdx.x >> 5) : 0); \
+  const size_t rstride = (size_t)gridDim.x * rpb;
+
+template <int TPR>
+__global__ void __launch_bounds__(kThreads) layernorm_fwd_kernel(
+    const float* __restrict__ x, const float* __restrict__ g, const float* __restrict__ b,
+    float* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, size_t rows,
+    size_t cols) {
+  ROW_SETUP(TPR)
+  for (size_t r = row0; r < rows; r += rstride) {  // uniform per row group
+    const float* xr = x + r * cols;
+    double s = 0.0;
+    for (size_t c = lane; c < cols; c += TPR) s += xr[c];
+    s = row_sum<TPR>(s, smd);
+    const float mu = (float)(s / (double)cols);
+    double v = 0.0;
+    for (size_t c = lane; c < cols; c += TPR) {
+      const double d = (double)xr[c] - mu;
+      v += d * d;
+    }
+    v = row_sum<TPR>(v, smd);
+    const float rs = 1.0f / sqrtf((float)(v / (double)cols) + 1e-5f);
+    if (lane == 0) { mean[r] = mu; rstd[r] = rs; }
+    for (size_t c = lane; c < cols; c += TPR) y[r * cols + c] = (xr[c] - mu) * rs * g[c] + b[c];
+  }
+}
+template <int TPR>
+__global__ void __launch_bounds__(kThreads) layernorm_bwd_kernel(
+    const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ g,
+    const float* __restrict__ mean, const float* __restrict__ rstd, float* __restrict__ dx,
+    size_t rows, size_t cols) {
+  ROW_SETUP(TPR)
+  const float inv_d = 1.0f / (float)cols;
+  for (size_t r = row0; r < rows; r += rstride) {
+    const float* dyr = dy + r * cols;
+    const float* xr = x + r * cols;
+    const float mu = mean[r], rs = rstd[r];
+    double sg = 0.0, sgx = 0.0;
+    for (size_t c = lane; c < cols; c += TPR) {
+      const float xh = (xr[c] - mu) * rs;
+      const float gg = dyr[c] * g[c];
+      sg += gg;
+      sgx += (double)gg * xh;
+    }
+    sg = row_sum<TPR>(sg, smd);
+    sgx = row_sum<TPR>(sgx, smd);
+    const float mg = (float)sg * inv_d, mgx = (float)sgx * inv_d;
+    for (size_t c = lane; c < cols; c += TPR) {
+      const float xh = (xr[c] - mu) * rs;
+      const float gg = dyr[c] * g[c];
+      dx[r * cols + c] = rs * (gg - mg - xh * mgx);
+    }
+  }
+}
+template <int TPR>
+__global__ void __launch_bounds__(kThreads) rmsnorm_fwd_kernel(
+    const float* __restrict__ x, const float* __restrict__ g, float* __restrict__ y,
+    float* __restrict__ rstd, size_t rows, size_t cols, int vec) {
+  ROW_SETUP(TPR)
+  for (size_t r = row0; r < rows; r += rstride) {
+    const float* xr = x + r * cols;
+    double ss = 0.0;
+    if (vec) {
+      for (size_t c = lane; c < (cols >> 2); c += TPR) {
+        const float4 v = reinterpret_cast<const float4*>(xr)[c];
+        ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+      }
+    } else {
+      for (size_t c = lane; c < cols; c += TPR) ss += (double)xr[c] * xr[c];
+    }
+    ss = row_sum<TPR>(ss, smd);
+    const float rs = 1.0f / sqrtf((float)(ss / (double)cols) + 1e-5f);
+    if (lane == 0) rstd[r] = rs;
+    if (vec) {
+      for (size_t c = lane; c < (cols >> 2); c += TPR) {
+        const float4 v = reinterpret_cast<const float4*>(xr)[c];
+        const float4 gg = reinterpret_cast<const float4*>(g)[c];
+        float4 o;
+        o.x = v.x * rs * gg.x; o.y = v.y * rs * gg.y; o.z = v.z * rs * gg.z; o.w = v.w * rs * gg.w;
+        reinterpret_cast<float4*>(y + r * cols)[c] = o;
+      }
+    } else {
+      for (size_t c = lane; c < cols; c += TPR) y[r * cols + c] = xr[c] * rs * g[c];
+    }
+  }
+}
+template <int TPR>
+__global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(
+    const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ g,
+    const float* __restrict__ rstd, float* __restrict__ dx, size_t rows, size_t cols, int vec) {
+  ROW_SETUP(TPR)
+  const float inv_d = 1.0f / (float)cols;
+  for (size_t r = row0; r < rows; r += rstride) {
+    const float* dyr = dy + r * cols;
+    const float* xr = x + r * cols;
+    const float rs = rstd[r];
+    double sgx = 0.0;
+    if (vec) {
+      for (size_t c = lane; c < (cols >> 2); c += TPR) {
+        const float4 d4 = reinterpret_cast<const float4*>(dyr)[c];
+        const float4 g4 = reinterpret_cast<const float4*>(g)[c];
+        const float4 x4 = reinterpret_cast<const float4*>(xr)[c];
+        sgx += (double)(d4.x * g4.x) * x4.x + (double)(d4.y * g4.y) * x4.y +
+               (double)(d4.z * g4.z) * x4.z + (double)(d4.w * g4.w) * x4.w;
+      }
+    } else {
+      for (size_t c = lane; c < cols; c += TPR) sgx += (double)(dyr[c] * g[c]) * xr[c];
+    }
+    sgx = row_sum<TPR>(sgx, smd);
+    const float mgx = (float)sgx * inv_d;
+    if (vec) {
+      for (size_t c = lane; c < (cols >> 2); c += TPR) {
+        const float4 d4 = reinterpret_cast<const float4*>(dyr)[c];
+        const float4 g4 = reinterpret_cast<const float4*>(g)[c];
+        const float4 x4 = reinterpret_cast<const float4*>(xr)[c];
+        float4 o;
+        o.x = rs * (d4.x * g4.x - x4.x * rs * rs * mgx);
+        o.y = rs * (d4.y * g4.y - x4.y * rs * rs * mgx);
+        o.z = rs * (d4.z * g4.z - x4.z * rs * rs * mgx);
+        o.w = rs * (d4.w * g4.w - x4.w * rs * rs * mgx);
+        reinterpret_cast<float4*>(dx + r * cols)[c] = o;
+      }
+    } else {
+      for (size_t c = lane; c < cols; c += TPR)
+        dx[r * cols + c] = rs * (dyr[c] * g[c] - xr[c] * rs * rs * mgx);
+    }
+  }
+}
+
+// ---- RoPE: one thread per interleaved pair ------------------------------------------------
+__global__ void __launch_bounds__(kThreads) rope_kernel(const float2* __restrict__ x,
+                                                        float2* __restrict__ y,
+                                                        const float2* __restrict__ table,
+                                                        size_t rows, size_t S, size_t H,
+                                                        size_t half, int backward) {
+  const size_t per_row = H * half;
+  const size_t n = rows * per_row;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / per_row, p = (i % per_row) % half;
+    const float2 cs = table[(row % S) * half + p];
+    const float2 v = x[i];
+    float2 o;
+    if (!backward) {
+      o.x = v.x * cs.x - v.y * cs.y;
+      o.y = v.x * cs.y + v.y * cs.x;
+    } else {
+      o.x = v.x * cs.x + v.y * cs.y;
+      o.y = -v.x * cs.y + v.y * cs.x;
+    }
+    y[i] = o;
+  }
+}
+// Odd head widths leave the last element of each head untouched by the rotation in
+// the reference loop (c + 1 < d); the validator only admits even d, so d is even here.
+
+// ---- attention row softmaxes: one warp per row -----------------------------------------------
+__global__ void __launch_bounds__(kThreads) causal_softmax_kernel(float* __restrict__ P,
+                                                                  size_t rows, size_t S) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t r = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    float* pr = P + r * S;
+    const size_t len = (r % S) + 1;
+    float mx = -INFINITY;
+    for (size_t j = lane; j < len; j += 32) mx = fmaxf(mx, pr[j]);
+    mx = warp_max(mx);
+    double den = 0.0;
+    for (size_t j = lane; j < len; j += 32) {
+      const float e = expf(pr[j] - mx);
+      pr[j] = e;
+      den += e;
+    }
+    den = warp_sum(den);
+    const float inv = 1.0f / (float)den;
+    for (size_t j = lane; j < len; j += 32) pr[j] *= inv;
+    for (size_t j = len + lane; j < S; j += 32) pr[j] = 0.0f;
+  }
+}
+__global__ void __launch_bounds__(kThreads) softmax_rows_bwd_kernel(const float* __restrict__ P,
+                                                                    const float* __restrict__ dP,
+                                                                    float* __restrict__ dS,
+                                                                    size_t rows, size_t cols) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t r = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const float* p = P + r * cols;
+    const float* g = dP + r * cols;
+    double dot = 0.0;
+    for (size_t c = lane; c < cols; c += 32) dot += (double)g[c] * p[c];
+    dot = warp_sum(dot);
+    const float sum = (float)dot;
+    for (size_t c = lane; c < cols; c += 32) dS[r * cols + c] = p[c] * (g[c] - sum);
+  }
+}
+
+// ---- losses -----------------------------------------------------------------------------------
+// The chunk geometry of the reference's ordered partial sums (parallel_for.h:55-67,
+// kernel_policy.h:37-47): grain raised so that at most 256 chunks exist.
+__host__ __device__ inline size_t chunk_grain(size_t n, size_t grain) {
+  if (grain == 0) grain = 1;
+  const size_t cap = (n + 255) / 256;
+  return grain < cap ? cap : grain;
+}
+inline size_t row_grain(size_t per_row, size_t budget) {
+  if (per_row == 0) return budget;
+  return budget / per_row > 0 ? budget / per_row : 1;
+}
+
+// Row softmax (f32 max-subtracted; the denominator is summed in double and rounded once)
+// + per-row loss term -log(max(p[label],1e-12)) in double, NaN kept. One block per row.
+template <int TPR>
+__global__ void __launch_bounds__(kThreads) xent_rows_kernel(
+    const float* __restrict__ logits, const int32_t* __restrict__ labels,
+    float* __restrict__ probs, double* __restrict__ terms, size_t N, size_t C, float inv_T) {
+  __shared__ double smd[8];
+  __shared__ float smf[8];
+  const int lane = TPR == 32 ? (threadIdx.x & 31) : threadIdx.x;
+  const size_t rpb = kThreads / TPR;
+  const size_t row0 = blockIdx.x * rpb + (TPR == 32 ? (threadIdx.x >> 5) : 0);
+  for (size_t n = row0; n < N; n += (size_t)gridDim.x * rpb) {
+    const float* z = logits + n * C;
+    float* p = probs + n * C;
+    float mx = -INFINITY;
+    for (size_t c = lane; c < C; c += TPR) mx = fmaxf(mx, z[c] * inv_T);
+    mx = row_max<TPR>(mx, smf);
+    double sum = 0.0;
+    for (size_t c = lane; c < C; c += TPR) {
+      const float e = expf(z[c] * inv_T - mx);
+      p[c] = e;
+      sum += e;
+    }
+    sum = row_sum<TPR>(sum, smd);
+    const float inv = 1.0f / (float)sum;
+    for (size_t c = lane; c < C; c += TPR) p[c] *= inv;
+    if (labels != nullptr) {
+      if (TPR != 32) __syncthreads();
+      else __syncwarp();
+      if (lane == 0) {
+        const float pl = p[(size_t)labels[n]];
+        const double safe = isnan(pl) ? (double)pl : (double)fmaxf(pl, 1e-12f);
+        terms[n] = -log(safe);
+      }
+    }
+  }
+}
+// terms[0..n) -> ordered chunk partials -> scalar mean. One thread per chunk, then one thread.
+__global__ void chunk_partials_kernel(const double* __restrict__ terms, double* __restrict__ partials,
+                                      size_t n, size_t grain) {
+  const size_t chunk = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  const size_t b = chunk * grain;
+  if (b >= n) return;
+  const size_t e = b + grain < n ? b + grain : n;
+  double t = 0.0;
+  for (size_t i = b; i < e; ++i) t += terms[i];
+  partials[chunk] = t;
+}
+__global__ void finish_mean_kernel(const double* __restrict__ partials, size_t chunks, double denom,
+                                   float* __restrict__ loss) {
+  double t = 0.0;
+  for (size_t c = 0; c < chunks; ++c) t += partials[c];
+  *loss = (float)(t / denom);
+}
+__global__ void __launch_bounds__(kThreads) xent_bwd_kernel(const float* __restrict__ probs,
+                                                            const int32_t* __restrict__ labels,
+                                                            const float* __restrict__ seed,
+                                                            float* __restrict__ d, size_t N, size_t C) {
+  const float scale = *seed / (float)N;
+  const size_t n = N * C;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / C, col = i % C;
+    float v = scale * probs[i];
+    if ((size_t)labels[row] == col) v -= scale;
+    d[i] = v;
+  }
+}
+__global__ void __launch_bounds__(kThreads) xent_bwd_vec_kernel(const float4* __restrict__ probs,
+                                                                const int32_t* __restrict__ labels,
+                                                                const float* __restrict__ seed,
+                                                                float4* __restrict__ d, size_t N,
+                                                                size_t C4) {
+  const float scale = *seed / (float)N;
+  const size_t n4 = N * C4;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / C4, c0 = (i % C4) * 4;
+    const size_t lab = (size_t)labels[row];
+    float4 p = probs[i];
+    p.x = scale * p.x; p.y = scale * p.y; p.z = scale * p.z; p.w = scale * p.w;
+    if (lab - c0 < 4) {
+      if (lab == c0) p.x -= scale;
+      else if (lab == c0 + 1) p.y -= scale;
+      else if (lab == c0 + 2) p.z -= scale;
+      else p.w -= scale;
+    }
+    d[i] = p;
+  }
+}
+__global__ void __launch_bounds__(kThreads) mse_terms_kernel(const float* __restrict__ p,
+                                                             const float* __restrict__ t,
+                                                             double* __restrict__ partials, size_t n,
+                                                             size_t grain) {
+  // one block per chunk; in-block tree in double, fixed order
+  __shared__ double smd[8];
+  const size_t b = blockIdx.x * grain;
+  const size_t e = b + grain < n ? b + grain : n;
+  double acc = 0.0;
+  for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) {
+    const double d = (double)p[i] - t[i];
+    acc += d * d;
+  }
+  acc = row_sum<kThreads>(acc, smd);
+  if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+}
+__global__ void __launch_bounds__(kThreads) mse_bwd_kernel(const float* __restrict__ p,
+                                                           const float* __restrict__ t,
+                                                           const float* __restrict__ seed,
+                                                           float* __restrict__ dp, size_t n) {
+  const float scale = 2.0f * *seed / (float)n;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    dp[i] = scale * (p[i] - t[i]);
+}
+// KL(p_t || p_s) row terms after both softmaxes are in place (loss.cc:108-125).
+template <int TPR>
+__global__ void __launch_bounds__(kThreads) kl_terms_kernel(const float* __restrict__ ps,
+                                                            const float* __restrict__ pt,
+                                                            double* __restrict__ terms, size_t N,
+                                                            size_t C) {
+  __shared__ double smd[8];
+  const int lane = TPR == 32 ? (threadIdx.x & 31) : threadIdx.x;
+  const size_t rpb = kThreads / TPR;
+  const size_t row0 = blockIdx.x * rpb + (TPR == 32 ? (threadIdx.x >> 5) : 0);
+  for (size_t n = row0; n < N; n += (size_t)gridDim.x * rpb) {
+    double acc = 0.0;
+    for (size_t c = lane; c < C; c += TPR) {
+      const float t = pt[n * C + c];
+      if (t <= 0.0f) continue;
+      const float raw = ps[n * C + c];
+      const double s = isnan(raw) ? (double)raw : (double)fmaxf(raw, 1e-12f);
+      acc += (double)t * (log((double)t) - log(s));
+    }
+    acc = row_sum<TPR>(acc, smd);
+    if (lane == 0) terms[n] = acc;
+  }
+}
+__global__ void __launch_bounds__(kThreads) kl_bwd_kernel(const float* __restrict__ ps,
+                                                          const float* __restrict__ pt,
+                                                          const float* __restrict__ seed,
+                                                          float* __restrict__ d, size_t n, float NT) {
+  const float scale = *seed / NT;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    d[i] = scale * (ps[i] - pt[i]);
+}
+
+// ---- optimiser family --------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) sumsq_chunks_kernel(const float* __restrict__ g,
+                                                                double* __restrict__ partials,
+                                                                size_t n, size_t grain) {
+  __shared__ double smd[8];
+  const size_t b = blockIdx.x * grain;
+  const size_t e = b + grain < n ? b + grain : n;
+  double acc = 0.0;
+  for (size_t i = b + threadIdx.x; i < e; i += blockDim.x) acc += (double)g[i] * (double)g[i];
+  acc = row_sum<kThreads>(acc, smd);
+  if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+}
+__global__ void clip_scale_kernel(const double* __restrict__ partials, size_t chunks, float max_norm,
+                                  float* __restrict__ scale_out) {
+  double sq = 0.0;
+  for (size_t c = 0; c < chunks; ++c) sq += partials[c];
+  const double norm = sqrt(sq);
+  float s = 1.0f;
+  if (!(norm <= (double)max_norm || norm == 0.0)) s = (float)((double)max_norm / norm);
+  *scale_out = s;
+}
+__global__ void __launch_bounds__(kThreads) scale_inplace_kernel(float* __restrict__ g,
+                                                                 const float* __restrict__ s,
+                                                                 size_t n) {
+  const float sc = *s;
+  if (sc == 1.0f) return;  // the reference returns before touching g
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    g[i] *= sc;
+}
+__global__ void __launch_bounds__(kThreads) sgd_kernel(float* __restrict__ p,
+                                                       const float* __restrict__ g, size_t n,
+                                                       const DevScalars* __restrict__ sc) {
+  const float lr = sc->lr, wd = sc->wd;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    p[i] -= lr * (g[i] + wd * p[i]);
+}
+__device__ __forceinline__ void adamw_one(float& p, float g, float& m, float& v, const DevScalars& s) {
+  const float mi = s.beta1 * m + s.om_b1 * g;
+  const float vi = s.beta2 * v + s.om_b2 * g * g;
+  m = mi;
+  v = vi;
+  const float mh = mi * s.inv_bc1, vh = vi * s.inv_bc2;
+  p -= s.lr * (mh / (sqrtf(vh) + s.eps) + s.wd * p);
+}
+__global__ void __launch_bounds__(kThreads) adamw_kernel(float* __restrict__ p,
+                                                         const float* __restrict__ g,
+                                                         float* __restrict__ m, float* __restrict__ v,
+                                                         size_t n, const DevScalars* __restrict__ scp,
+                                                         int vec) {
+  const DevScalars s = *scp;
+  if (vec) {
+    const size_t n4 = n >> 2;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4;
+         i += (size_t)gridDim.x * blockDim.x) {
+      float4 P = reinterpret_cast<float4*>(p)[i], M = reinterpret_cast<float4*>(m)[i],
+             V = reinterpret_cast<float4*>(v)[i];
+      const float4 G = reinterpret_cast<const float4*>(g)[i];
+      adamw_one(P.x, G.x, M.x, V.x, s); adamw_one(P.y, G.y, M.y, V.y, s);
+      adamw_one(P.z, G.z, M.z, V.z, s); adamw_one(P.w, G.w, M.w, V.w, s);
+      reinterpret_cast<float4*>(p)[i] = P;
+      reinterpret_cast<float4*>(m)[i] = M;
+      reinterpret_cast<float4*>(v)[i] = V;
+    }
+    for (size_t i = (n4 << 2) + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+      adamw_one(p[i], g[i], m[i], v[i], s);
+  } else {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+      adamw_one(p[i], g[i], m[i], v[i], s);
+  }
+}
+
+// ---- gate metrics ---------------------------------------------------------------------------
+// Exact argmax accuracy: the first column holding the row maximum wins, as the
+// reference's strict '>' scan does. One warp per row; integer atomics only.
+__global__ void __launch_bounds__(kThreads) count_correct_kernel(const float* __restrict__ probs,
+                                                                 const int32_t* __restrict__ labels,
+                                                                 size_t real, size_t C,
+                                                                 unsigned long long* counter) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t r = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); r < real; r += warps) {
+    const float* row = probs + r * C;
+    float best = -INFINITY;
+    size_t arg = C;  // C = "no column yet"
+    for (size_t c = lane; c < C; c += 32) {
+      const float v = row[c];
+      if (v > best || (arg == C && v == best)) { best = v; arg = c; }  // NaN never enters
+    }
+    // a NaN entry never wins a strict '>' comparison; column 0 is the scan's seed
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const size_t oa = __shfl_xor_sync(0xffffffffu, (unsigned long long)arg, o);
+      if (oa != C && (arg == C || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
+    }
+    if (lane == 0) {
+      // the reference seeds argmax = 0 and replaces only on row[c] > row[argmax]
+      if (!(row[0] == row[0])) arg = 0;  // NaN seed is never replaced
+      const int32_t lab = labels[r];
+      if (lab >= 0 && (size_t)lab == arg) atomicAdd(counter, 1ull);
+    }
+  }
+}
+__global__ void __launch_bounds__(kThreads) count_nonfinite_kernel(const float* __restrict__ x, size_t n,
+                                                                   unsigned long long* counter) {
+  unsigned long long bad = 0;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    if (!isfinite(x[i])) ++bad;
+  if (bad) atomicAdd(counter, bad);
+}
+
+// ---- gradient sets --------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) pack_kernel(uint8_t* __restrict__ arena,
+                                                        const Span* __restrict__ spans, size_t nspans,
+                                                        float* __restrict__ packed, int unpack,
+                                                        size_t total) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    // binary search for the span holding packed index i
+    size_t lo = 0, hi = nspans;
+    while (hi - lo > 1) {
+      const size_t mid = (lo + hi) >> 1;
+      if (spans[mid].packed_off <= i) lo = mid; else hi = mid;
+    }
+    float* a = reinterpret_cast<float*>(arena + spans[lo].arena_off) + (i - spans[lo].packed_off);
+    if (unpack) *a = packed[i]; else packed[i] = *a;
+  }
+}
+// Fixed binary tree over the set index: level by level, set i += set i+stride.
+__global__ void __launch_bounds__(kThreads) tree_level_kernel(float* __restrict__ sets, size_t fps,
+                                                              size_t count, size_t stride) {
+  const size_t pairs = (count + 2 * stride - 1) / (2 * stride);
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < pairs * fps;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t pr = i / fps, e = i % fps;
+    const size_t a = pr * 2 * stride, b = a + stride;
+    if (b < count) sets[a * fps + e] = sets[a * fps + e] + sets[b * fps + e];
+  }
+}
+
+}  // namespace
+
+// ================================ launchers ========================================================
+int add(const float* x, const float* y, float* o, size_t n, cudaStream_t st) {
+  return launch_ew<2>(FAdd{}, x, y, o, n, st);
+}
+int mul(const float* x, const float* y, float* o, size_t n, cudaStream_t st) {
+  return launch_ew<2>(FMul{}, x, y, o, n, st);
+}
+int scale(const float* x, float* o, float alpha, size_t n, cudaStream_t st) {
+  return launch_ew<1>(FScale{alpha}, x, nullptr, o, n, st);
+}
+int act_fwd(int act, const float* x, float* o, size_t n, cudaStream_t st) {
+  return launch_ew<1>(FAct{act}, x, nullptr, o, n, st);
+}
+int act_bwd(int act, const float* dy, const float* x, float* dx, size_t n, cudaStream_t st) {
+  return launch_ew<2>(FActBwd{act}, dy, x, dx, n, st);
+}
+int fill(float* d, float v, size_t n, cudaStream_t st) {
+  return launch_ew<0>(FFill{v}, nullptr, nullptr, d, n, st);
+}
+int copy(const float* s, float* d, size_t n, cudaStream_t st) {
+  if (n == 0) return 0;
+  cudaMemcpyAsync(d, s, n * sizeof(float), cudaMemcpyDeviceToDevice, st);
+  return 1;
+}
+int add_bias(const float* x, const float* b, float* o, size_t rows, size_t cols, cudaStream_t st) {
+  const size_t n = rows * cols;
+  if (n == 0) return 0;
+  bias_act_kernel<<<grid_for(n / 4 + 1, kThreads), kThreads, 0, st>>>(x, b, o, rows, cols, 0);
+  return 1;
+}
+int bias_act(float* c, const float* bias, size_t rows, size_t cols, int act, cudaStream_t st) {
+  const size_t n = rows * cols;
+  if (n == 0 || (bias == nullptr && act == 0)) return 0;
+  bias_act_kernel<<<grid_for(n / 4 + 1, kThreads), kThreads, 0, st>>>(c, bias, c, rows, cols, act);
+  return 1;
+}
+int embed(const int32_t* tok, const float* table, float* o, size_t rows, size_t dim, cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int vec = (dim % 4 == 0) && aligned16(table) && aligned16(o);
+  embed_kernel<<<grid_for(rows, kThreads / 32, 16), kThreads, 0, st>>>(tok, table, o, rows, dim, vec);
+  return 1;
+}
+int reduce_rows(const float* dy, float* db, size_t rows, size_t cols, cudaStream_t st) {
+  if (cols == 0) return 0;
+  reduce_rows_kernel<<<(unsigned)((cols + 127) / 128), 128, 0, st>>>(dy, db, rows, cols);
+  return 1;
+}
+
+#define ROW_LAUNCH(KERNEL, rows, cols, ...)                                                 \
+  do {                                                                                      \
+    if ((cols) <= 2048)                                                                     \
+      KERNEL<32><<<grid_for((rows), kThreads / 32, 16), kThreads, 0, st>>>(__VA_ARGS__);    \
+    else                                                                                    \
+      KERNEL<kThreads><<<grid_for((rows), 1, 16), kThreads, 0, st>>>(__VA_ARGS__);          \
+  } while (0)
+
+int layernorm_fwd(const float* x, const float* g, const float* b, float* y, float* mean,
+                  float* rstd, size_t rows, size_t cols, cudaStream_t st) {
+  if (rows == 0) return 0;
+  ROW_LAUNCH(layernorm_fwd_kernel, rows, cols, x, g, b, y, mean, rstd, rows, cols);
+  return 1;
+}
+int layernorm_bwd(const float* dy, const float* x, const float* g, const float* mean,
+                  const float* rstd, float* dx, size_t rows, size_t cols, cudaStream_t st) {
+  if (rows == 0) return 0;
+  ROW_LAUNCH(layernorm_bwd_kernel, rows, cols, dy, x, g, mean, rstd, dx, rows, cols);
+  return 1;
+}
+int rmsnorm_fwd(const float* x, const float* g, float* y, float* rstd, size_t rows, size_t cols,
+                cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int vec = cols % 4 == 0 && aligned16(x) && aligned16(g) && aligned16(y);
+  ROW_LAUNCH(rmsnorm_fwd_kernel, rows, cols, x, g, y, rstd, rows, cols, vec);
+  return 1;
+}
+int rmsnorm_bwd(const float* dy, const float* x, const float* g, const float* rstd, float* dx,
+                size_t rows, size_t cols, cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int vec = cols % 4 == 0 && aligned16(x) && aligned16(g) && aligned16(dy) && aligned16(dx);
+  ROW_LAUNCH(rmsnorm_bwd_kernel, rows, cols, dy, x, g, rstd, dx, rows, cols, vec);
+  return 1;
+}
+int rope(const float* x, float* y, const float2* table, size_t B, size_t S, size_t H, size_t d,
+         int backward, cudaStream_t st) {
+  const size_t n = B * S * H * (d / 2);
+  if (n == 0) return 0;
+  rope_kernel<<<grid_for(n, kThreads), kThreads, 0, st>>>(
+      reinterpret_cast<const float2*>(x), reinterpret_cast<float2*>(y), table, B * S, S, H, d / 2,
+      backward);
+  return 1;
+}
+int causal_softmax_rows(float* P, size_t BH, size_t S, cudaStream_t st) {
+  const size_t rows = BH * S;
+  if (rows == 0) return 0;
+  causal_softmax_kernel<<<grid_for(rows, kThreads / 32, 16), kThreads, 0, st>>>(P, rows, S);
+  return 1;
+}
+int softmax_rows_bwd(const float* P, const float* dP, float* dS, size_t rows, size_t cols,
+                     cudaStream_t st) {
+  if (rows == 0) return 0;
+  softmax_rows_bwd_kernel<<<grid_for(rows, kThreads / 32, 16), kThreads, 0, st>>>(P, dP, dS, rows, cols);
+  return 1;
+}
+
+size_t loss_scratch_doubles(size_t rows_or_elems) { return rows_or_elems + 256; }
+
+static int finish_loss(double* terms, size_t n_terms, size_t grain, double denom, float* loss,
+                       cudaStream_t st) {
+  // terms -> chunk partials (chunk geometry = the reference's) -> ordered sum -> mean
+  double* partials = terms + n_terms;
+  const size_t chunks = (n_terms + grain - 1) / grain;
+  chunk_partials_kernel<<<(unsigned)((chunks + 63) / 64), 64, 0, st>>>(terms, partials, n_terms, grain);
+  finish_mean_kernel<<<1, 1, 0, st>>>(partials, chunks, denom, loss);
+  return 2;
+}
+int xent_fwd(const float* logits, const int32_t* labels, float* loss, float* probs, size_t N,
+             size_t C, double* scratch, cudaStream_t st) {
+  if (N == 0) return 0;
+  if (C <= 1024)
+    xent_rows_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(logits, labels, probs,
+                                                                             scratch, N, C, 1.0f);
+  else
+    xent_rows_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(logits, labels, probs,
+                                                                       scratch, N, C, 1.0f);
+  return 1 + finish_loss(scratch, N, chunk_grain(N, row_grain(C, 4096)), (double)N, loss, st);
+}
+int xent_bwd(const float* probs, const int32_t* labels, const float* seed, float* dlogits,
+             size_t N, size_t C, cudaStream_t st) {
+  if (N * C == 0) return 0;
+  if (C % 4 == 0 && aligned16(probs) && aligned16(dlogits))
+    xent_bwd_vec_kernel<<<grid_for(N * C / 4, kThreads), kThreads, 0, st>>>(
+        reinterpret_cast<const float4*>(probs), labels, seed, reinterpret_cast<float4*>(dlogits), N,
+        C / 4);
+  else
+    xent_bwd_kernel<<<grid_for(N * C, kThreads), kThreads, 0, st>>>(probs, labels, seed, dlogits, N, C);
+  return 1;
+}
+int mse_fwd(const float* p, const float* t, float* loss, size_t n, double* scratch, cudaStream_t st) {
+  if (n == 0) return 0;
+  const size_t grain = chunk_grain(n, 32768);
+  const size_t chunks = (n + grain - 1) / grain;
+  mse_terms_kernel<<<(unsigned)chunks, kThreads, 0, st>>>(p, t, scratch, n, grain);
+  finish_mean_kernel<<<1, 1, 0, st>>>(scratch, chunks, (double)n, loss);
+  return 2;
+}
+int mse_bwd(const float* p, const float* t, const float* seed, float* dp, size_t n, cudaStream_t st) {
+  if (n == 0) return 0;
+  mse_bwd_kernel<<<grid_for(n, kThreads), kThreads, 0, st>>>(p, t, seed, dp, n);
+  return 1;
+}
+int kl_fwd(const float* s, const float* t, float* loss, float* ps, float* pt, size_t N, size_t C,
+           float T, double* scratch, cudaStream_t st) {
+  if (N == 0) return 0;
+  const float inv_T = 1.0f / T;
+  if (C <= 1024) {
+    xent_rows_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(s, nullptr, ps, scratch, N, C, inv_T);
+    xent_rows_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(t, nullptr, pt, scratch, N, C, inv_T);
+    kl_terms_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(ps, pt, scratch, N, C);
+  } else {
+    xent_rows_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(s, nullptr, ps, scratch, N, C, inv_T);
+    xent_rows_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(t, nullptr, pt, scratch, N, C, inv_T);
+    kl_terms_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(ps, pt, scratch, N, C);
+  }
+  return 3 + finish_loss(scratch, N, chunk_grain(N, row_grain(C, 4096)), (double)N, loss, st);
+}
+int kl_bwd(const float* ps, const float* pt, const float* seed, float* d, size_t N, size_t C,
+           float T, cudaStream_t st) {
+  if (N * C == 0) return 0;
+  kl_bwd_kernel<<<grid_for(N * C, kThreads), kThreads, 0, st>>>(ps, pt, seed, d, N * C, (float)N * T);
+  return 1;
+}
+int clip_norm(float* g, size_t n, float max_norm, double* scratch, cudaStream_t st) {
+  if (n == 0) return 0;
+  const size_t grain = chunk_grain(n, 32768);
+  const size_t chunks = (n + grain - 1) / grain;
+  float* scale_slot = reinterpret_cast<float*>(scratch + 256);
+  sumsq_chunks_kernel<<<(unsigned)chunks, kThreads, 0, st>>>(g, scratch, n, grain);
+  clip_scale_kernel<<<1, 1, 0, st>>>(scratch, chunks, max_norm, scale_slot);
+  scale_inplace_kernel<<<grid_for(n, kThreads), kThreads, 0, st>>>(g, scale_slot, n);
+  return 3;
+}
+int sgd(float* p, const float* g, size_t n, const DevScalars* sc, cudaStream_t st) {
+  if (n == 0) return 0;
+  sgd_kernel<<<grid_for(n, kThreads), kThreads, 0, st>>>(p, g, n, sc);
+  return 1;
+}
+int adamw(float* p, const float* g, float* m, float* v, size_t n, const DevScalars* sc,
+          cudaStream_t st) {
+  if (n == 0) return 0;
+  const int vec = aligned16(p) && aligned16(g) && aligned16(m) && aligned16(v);
+  adamw_kernel<<<grid_for(n / (vec ? 4 : 1) + 1, kThreads), kThreads, 0, st>>>(p, g, m, v, n, sc, vec);
+  return 1;
+}
+int count_correct(const float* probs, const int32_t* labels, size_t real, size_t C,
+                  unsigned long long* counter, cudaStream_t st) {
+  if (real == 0) return 0;
+  count_correct_kernel<<<grid_for(real, kThreads / 32, 16), kThreads, 0, st>>>(probs, labels, real, C, counter);
+  return 1;
+}
+int count_nonfinite(const float* x, size_t n, unsigned long long* counter, cudaStream_t st) {
+  if (n == 0) return 0;
+  count_nonfinite_kernel<<<grid_for(n, kThreads), kThreads, 0, st>>>(x, n, counter);
+  return 1;
+}
+int pack_spans(const uint8_t* arena, const Span* spans_dev, size_t nspans, float* packed, int unpack,
+               size_t total, cudaStream_t st) {
+  if (total == 0) return 0;
+  pack_kernel<<<grid_for(total, kThreads), kThreads, 0, st>>>(const_cast<uint8_t*>(arena), spans_dev,
+                                                             nspans, packed, unpack, total);
+  return 1;
+}
+int tree_sum(float* sets, size_t fps, size_t count, float scale_v, cudaStream_t st) {
+  int launches = 0;
+  for (size_t stride = 1; stride < count; stride <<= 1) {
+    const size_t pairs = (count + 2 * stride - 1) / (2 * stride);
+    tree_level_kernel<<<grid_for(pairs * fps, kThreads), kThreads, 0, st>>>(sets, fps, count, stride);
+    ++launches;
+  }
+  if (scale_v != 1.0f) launches += scale(sets, sets, scale_v, fps, st);
+  return launches;
+}
+
+}  // namespace k
+}  // namespace seeml_b200

@@ -277,7 +277,7 @@ def assemble_plan(header: PlanHeader, train: np.ndarray, merge: np.ndarray, eval
         persist_init.tobytes()
     blob[header.emit_table_offset:header.emit_table_offset + emit.nbytes] = emit.tobytes()
     hfn = hasher or (lambda b, o: content_hash64(b, o))
-    header.plan_hash = hfn(bytes(blob), PLAN_HASH_OFFSET)
+    header.plan_hash = hfn(blob, PLAN_HASH_OFFSET)
     blob[PLAN_HASH_OFFSET:PLAN_HASH_OFFSET + 8] = struct.pack("<Q", header.plan_hash)
     return bytes(blob)
 
