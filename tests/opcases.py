@@ -315,7 +315,7 @@ def loss_cases(rng):
         ar, r = L.done()
         cases.append(Case(f"XENT_FWD_{N}x{C}", _ins(Op.XENT_FWD, [rl, rlab, loss, probs], [N, C]), ar, r,
                           {"loss": (loss, 1, np.float32), "probs": (probs, N * C, np.float32)},
-                          rtol=1e-5, atol=1e-7))
+                          rtol=2e-4, atol=1e-7))   # the reference sums the denominator serially in f32
         p = np.exp(logits - logits.max(1, keepdims=True))
         p = (p / p.sum(1, keepdims=True)).astype(np.float32)
         L = Layout()
@@ -332,7 +332,7 @@ def loss_cases(rng):
         cases.append(Case(f"KL_FWD_{N}x{C}",
                           _ins(Op.KL_FWD, [rs, rt, loss, ps], [pt, F.pack32(N, C), F.f32_bits(2.0)]), ar, r,
                           {"loss": (loss, 1, np.float32), "ps": (ps, N * C, np.float32),
-                           "pt": (pt, N * C, np.float32)}, rtol=1e-5, atol=1e-7))
+                           "pt": (pt, N * C, np.float32)}, rtol=2e-4, atol=1e-7))
         L = Layout()
         rps, rpt, seed = L.put(p), L.put(p[::-1].copy()), L.put(np.array([0.5], np.float32))
         d = L.out(N * C)
