@@ -287,20 +287,22 @@ def run_ours(args, cfg):
     value = tokens / (ms_step * 1e-3)
 
     # ---- arm B: end to end through the public API from host buffers --------------------------
-    e2e_steps = max(1, min(args.steps, 3))
-    hb = [batches_for(100 + s) for s in range(e2e_steps + 1)]
-    tr.step(*hb[0])
-    barrier()
-    with torch.cuda.stream(tr.stream):
-        ev0.record()
-        for s in range(e2e_steps):
-            loss_b = tr.step(*hb[1 + s])
-        ev1.record()
-    barrier()
-    e2e_ms = max_over_ranks(ev0.elapsed_time(ev1)) / e2e_steps
-    e2e = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
-           "h2d_bytes_per_step": int(tr.h2d_bytes * world), "d2h_bytes_per_step": int(tr.d2h_bytes * world),
-           "ms_per_step": e2e_ms, "steps": e2e_steps}
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(1, min(args.steps, 3))
+        hb = [batches_for(100 + s) for s in range(e2e_steps + 1)]
+        tr.step(*hb[0])
+        barrier()
+        with torch.cuda.stream(tr.stream):
+            ev0.record()
+            for s in range(e2e_steps):
+                tr.step(*hb[1 + s])
+            ev1.record()
+        barrier()
+        e2e_ms = max_over_ranks(ev0.elapsed_time(ev1)) / e2e_steps
+        e2e = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": int(tr.h2d_bytes * world), "d2h_bytes_per_step": int(tr.d2h_bytes * world),
+               "ms_per_step": e2e_ms, "steps": e2e_steps}
 
     if rank == 0:
         hbm, tf_burst, tf_sust, src = measured_peaks()
@@ -308,7 +310,7 @@ def run_ours(args, cfg):
         # roofline of the dominant kernel: the largest GEMM instruction of the stream, timed
         # alone with CUDA events on the stream it is launched on
         roof = None
-        if top is not None:
+        if top is not None and not args.no_e2e:
             fl, ins = top
             m, n, k = (int(v) for v in ins["out"])
             ctx = Context((m * k + k * n + m * n) * 4 + 4096, None, device=local_rank, gemm=gemm)
@@ -368,8 +370,12 @@ def main():
     ap.add_argument("--gemm", default="tf32x3", choices=["tf32x3", "bf16", "simt", "tf32"])
     ap.add_argument("--fused", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--chunks", type=int, default=0, help="override chunks per step (profiling aid)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (profiling aid)")
     args = ap.parse_args()
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.chunks:
+        cfg["chunks"] = args.chunks
     if args.impl == "reference":
         run_reference(args, cfg)
     else:

@@ -130,6 +130,39 @@ k::GemmDesc gemm_desc_of(const Exec& x, const Instr& ins) {
   return d;
 }
 
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Rank-r shapes go to the dedicated kernels. Returns the launch count, or 0 when the
+// instruction is not one of those shapes.
+int try_skinny(const Exec& x, const Instr& ins, bool launch, uint64_t* ws_need) {
+  if (ins.opcode != kGemmNN && ins.opcode != kGemmNT && ins.opcode != kGemmTN) return 0;
+  if (ins.flags != 0) return 0;
+  const uint64_t M64 = ins.out[0], N64 = ins.out[1], K64 = ins.out[2];
+  if (M64 > 0x7FFFFFFF || N64 > 0x7FFFFFFF || K64 > 0x7FFFFFFF) return 0;
+  if (M64 * N64 > 0x7FFFFFFF) return 0;
+  const int M = (int)M64, N = (int)N64, K = (int)K64;
+  const float* A = x.R(ins.in[0]);
+  const float* B = x.R(ins.in[1]);
+  float* C = x.W(ins.in[2]);
+  cudaStream_t st = x.c->stream;
+  if (ins.opcode == kGemmTN) {
+    // C[M,N] = A[K,M]^T B[K,N]; the reduction runs over the K rows
+    if (N <= M && k::skinny_tn_ok(K, M, N)) {
+      if (ws_need) *ws_need = k::skinny_tn_workspace_floats(K, M, N);
+      return launch ? k::skinny_tn(A, B, C, x.c->gemm_ws, K, M, N, 1, 1.0f, st) : 2;
+    }
+    if (M < N && k::skinny_tn_ok(K, N, M)) {
+      if (ws_need) *ws_need = k::skinny_tn_workspace_floats(K, N, M);
+      return launch ? k::skinny_tn(B, A, C, x.c->gemm_ws, K, N, M, 0, 1.0f, st) : 2;
+    }
+    return 0;
+  }
+  const int b_is_nk = ins.opcode == kGemmNT;
+  if (k::skinny_n_ok(M, N, K) && al16(A)) return launch ? k::skinny_n(A, B, C, M, N, K, b_is_nk, 1.0f, st) : 1;
+  if (k::skinny_k_ok(M, N, K) && al16(C)) return launch ? k::skinny_k(A, B, nullptr, C, M, N, K, b_is_nk, 1.0f, st) : 1;
+  return 0;
+}
+
 uint64_t scratch_need_loss(const Instr& ins) {
   switch (ins.opcode) {
     case kXentFwd: return k::loss_scratch_doubles(ins.out[0]);
@@ -148,6 +181,7 @@ int dispatch(Exec& x, const Instr& ins) {
   switch (ins.opcode) {
     case kNop: break;
     case kGemmNN: case kGemmNT: case kGemmTN: case kGemmAccNN: case kGemmNNQ8: case kGemmNTQ8: {
+      if ((n = try_skinny(x, ins, true, nullptr)) != 0) break;
       int tc = gemm_tensor_core(c, ins, &n);
       if (tc < 0) return 1;
       if (tc == 0) {
@@ -318,7 +352,9 @@ int prepare_instr(seeml_b200_ctx* c, const Instr& ins, uint64_t* loss_need, uint
   if (ins.opcode >= kGemmNN && ins.opcode <= kGemmAccNN) {
     Exec x{c};
     const k::GemmDesc d = gemm_desc_of(x, ins);
-    const uint64_t w = k::gemm_simt_workspace_floats(d);
+    uint64_t w = k::gemm_simt_workspace_floats(d);
+    uint64_t wsk = 0;
+    if (try_skinny(x, ins, false, &wsk) != 0 && wsk > w) w = wsk;
     if (w > *ws_need) *ws_need = w;
     if (int r = gemm_tensor_core_prepare(c, ins)) return r;
   }
@@ -591,6 +627,8 @@ int seeml_b200_sync(seeml_b200_ctx* c) {
   CU(cudaSetDevice(c->device), "cudaSetDevice");
   CU(cudaStreamSynchronize(c->stream), "stream sync");
   CU(cudaGetLastError(), "kernel execution");
+  if (const int code = gemm_tensor_core_error(c))
+    return fail("UpdateEngine: tensor-core GEMM gave up on a bounded wait (code " + std::to_string(code) + ")");
   return 0;
 }
 int seeml_b200_ctx_enable_timing(seeml_b200_ctx* c, int on) {

@@ -35,6 +35,7 @@ namespace seeml_b200 {
 int gemm_tensor_core(seeml_b200_ctx* c, const Instr& ins, int* launches);
 int gemm_tensor_core_prepare(seeml_b200_ctx* c, const Instr& ins);
 void gemm_tensor_core_release(seeml_b200_ctx* c);
+int gemm_tensor_core_error(seeml_b200_ctx* c);
 
 struct Program {
   std::vector<Instr> instrs;

@@ -106,5 +106,20 @@ struct GemmDesc {
 size_t gemm_simt_workspace_floats(const GemmDesc& d);
 int gemm_simt(const GemmDesc& d, float* workspace, cudaStream_t st);
 
+// ---- GEMMs with one tiny dimension (the LoRA factors), kernels_skinny.cu -------------------
+bool skinny_n_ok(int M, int n, int K);
+bool skinny_k_ok(int M, int N, int k);
+bool skinny_tn_ok(int T, int big, int small);
+size_t skinny_tn_workspace_floats(int T, int big, int small);
+// out[M,n] = alpha * A[M,K] . B, B given [K,n] (b_is_nk = 0) or [n,K] (b_is_nk = 1)
+int skinny_n(const float* A, const float* B, float* out, int M, int n, int K, int b_is_nk, float alpha,
+             cudaStream_t st);
+// out[M,N] = alpha * A[M,k] . B (+ addend[M,N]), B given [k,N] or [N,k]
+int skinny_k(const float* A, const float* B, const float* addend, float* out, int M, int N, int k, int b_is_nk,
+             float alpha, cudaStream_t st);
+// R[s,b] = alpha * sum_t S[t,s] * W[t,b]; stored [small,big], or [big,small] when transposed
+int skinny_tn(const float* W, const float* S, float* out, float* workspace, int T, int big, int small,
+              int transposed, float alpha, cudaStream_t st);
+
 }  // namespace k
 }  // namespace seeml_b200

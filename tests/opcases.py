@@ -108,6 +108,23 @@ def gemm_cases(rng, big=False):
         ar, r = L.done()
         cases.append(Case(f"GEMM_TN_splitk_{M}x{N}x{K}", _ins(Op.GEMM_TN, [a, b, c], [M, N, K]), ar, r,
                           {"C": (c, M * N, np.float32)}, rtol=2e-3, atol=2e-3))
+    # rank-r shapes: narrow output, tiny reduction, long skinny TN (the LoRA factor GEMMs)
+    for (M, N, K) in [(300, 16, 520), (200, 8, 132), (70, 32, 256), (200, 132, 16), (65, 260, 8), (40, 68, 31)]:
+        for op in (Op.GEMM_NN, Op.GEMM_NT):
+            L = Layout()
+            a = L.put(_rn(rng, M, K))
+            b = L.put(_rn(rng, N, K) if op == Op.GEMM_NT else _rn(rng, K, N))
+            c = L.out(M * N)
+            ar, r = L.done()
+            cases.append(Case(f"{op.name}_skinny_{M}x{N}x{K}", _ins(op, [a, b, c], [M, N, K]), ar, r,
+                              {"C": (c, M * N, np.float32)}))
+    for (M, N, K) in [(16, 200, 2100), (200, 8, 1500), (130, 64, 1024), (4, 70, 1030)]:
+        L = Layout()
+        a, b = L.put(_rn(rng, K, M)), L.put(_rn(rng, K, N))
+        c = L.out(M * N)
+        ar, r = L.done()
+        cases.append(Case(f"GEMM_TN_skinny_{M}x{N}x{K}", _ins(Op.GEMM_TN, [a, b, c], [M, N, K]), ar, r,
+                          {"C": (c, M * N, np.float32)}, rtol=1e-3, atol=5e-4))
     # fused epilogues on GEMM_NN: bias and/or activation
     for act in (0, 1, 2, 3):
         for bias in (False, True):
@@ -362,7 +379,7 @@ def loss_cases(rng):
     loss, probs = L.out(1), L.out(24)
     ar, r = L.done()
     cases.append(Case("XENT_FWD_nan", _ins(Op.XENT_FWD, [rl, rlab, loss, probs], [4, 6]), ar, r,
-                      {"loss": (loss, 1, np.float32)}))
+                      {"loss": (loss, 1, np.float32), "probs": (probs, 24, np.float32)}))
     return cases
 
 
