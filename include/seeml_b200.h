@@ -136,6 +136,24 @@ int seeml_b200_sync(seeml_b200_ctx* ctx);
 int seeml_b200_ctx_enable_timing(seeml_b200_ctx* ctx, int on);
 int seeml_b200_last_run_ms(seeml_b200_ctx* ctx, float* ms);
 
+/* --------------------------------------------- allocation-free softmax cross-entropy --
+ * No counterpart in the reference. For hosts that may not call the CUDA allocator (the
+ * device's memory is already owned by their own pool, or an allocation's implicit
+ * synchronisation is not acceptable where they call from): the same kernels as the
+ * kXentFwd instruction (loss = -(1/rows) sum log softmax(logits)[label], probs cached),
+ * with the reduction scratch held in a fixed array inside the library, so the call only
+ * launches kernels. All pointers are DEVICE pointers the caller owns; `stream` is a
+ * cudaStream_t (NULL = the default stream); the call is asynchronous on that stream.
+ * Limit: rows <= 65536 per call, larger calls are refused with an error. Every GPU that
+ * loads the library holds the array (about 0.5 MiB) until the process exits.
+ * The first call on each device looks the array's device address up
+ * (cudaGetSymbolAddress) with that device current: make that first call outside any
+ * stream capture. Every call uses the same array: two calls that may overlap on the
+ * GPU (different streams, no ordering between them) race on it. Nothing in the array
+ * has to start at zero; each call overwrites what it reads. */
+int seeml_b200_xent_fwd_noalloc(const float* logits, const int32_t* labels, float* loss, float* probs,
+                                uint64_t rows, uint64_t classes, void* stream);
+
 /* ------------------------------------------------- data-parallel gradient sets --
  * No counterpart in the reference (single process). A gradient set is the list of
  * (arena offset, float count) pairs of the optimiser instructions' gradient

@@ -69,6 +69,7 @@ SIGNATURES = {
     "seeml_b200_sync": (INT, [vp]),
     "seeml_b200_ctx_enable_timing": (INT, [vp, INT]),
     "seeml_b200_last_run_ms": (INT, [vp, C.POINTER(f32)]),
+    "seeml_b200_xent_fwd_noalloc": (INT, [vp, vp, vp, vp, u64, u64, vp]),
     "seeml_b200_grads_pack": (INT, [vp, vp, vp, u64, vp]),
     "seeml_b200_grads_unpack": (INT, [vp, vp, vp, u64, vp]),
     "seeml_b200_tree_sum": (INT, [vp, vp, u64, u64, f32]),

@@ -32,7 +32,7 @@ EXTRA = {"kernels_mem.cu": ["-fmad=false"]}
 GXX_FLAGS = ["-O2", "-std=c++23", "-fPIC", "-pthread", "-I" + INCLUDE, "-I" + CSRC,
              "-I" + os.path.join(CUDA, "include"), "-Wall", "-Wextra", "-Wno-unused-parameter"]
 
-CU_SRCS = ["kernels_mem.cu", "kernels_gemm_simt.cu", "kernels_skinny.cu", "gemm_tc.cu", "backend.cu"]
+CU_SRCS = ["kernels_mem.cu", "kernels_gemm_simt.cu", "kernels_skinny.cu", "gemm_tc.cu", "backend.cu", "xent_noalloc.cu"]
 CC_SRCS = ["validate.cc", "dataset.cc", "engine.cc"]
 
 
