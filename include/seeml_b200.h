@@ -103,6 +103,20 @@ int seeml_b200_program_run(seeml_b200_ctx* ctx, int program_id, uint64_t begin,
 int seeml_b200_exec_one(seeml_b200_ctx* ctx, const void* instr, uint32_t plan_version,
                         const seeml_b200_scalars* scalars);
 
+/* The fused GEMM the LoRA groups lower to, as one call on arena offsets:
+ *   C[M,N] = (addend[M,N] +) A[M,K] . B[N,K]^T (+ A2[M,K2] . B2[N,K2]^T)
+ * i.e. a forward C' = X.W + (alpha/r)(X.A).B with B = W^T, A2 = X.A, B2 = (alpha/r) B^T, or a
+ * backward dX = dC'.W^T + dT.A^T. Stands in for the gemm.nn / gemm.nt + scale + add.ew
+ * sequences of lora_grafter.cc:130-159 and autodiff.cc:71-91. Offsets are arena byte
+ * offsets (a2/b2 ignored when k2 == 0; addend_offset == UINT64_MAX means none). Runs on the
+ * tensor cores when the shape allows, else on the CUDA cores; asynchronous. */
+typedef struct seeml_b200_fused_gemm {
+  uint64_t a_offset, b_offset, c_offset, m, n, k;
+  uint64_t a2_offset, b2_offset, k2;
+  uint64_t addend_offset;
+} seeml_b200_fused_gemm;
+int seeml_b200_gemm_fused(seeml_b200_ctx* ctx, const seeml_b200_fused_gemm* g);
+
 /* Arena transfers (synchronous with respect to the compute stream). */
 int seeml_b200_h2d(seeml_b200_ctx* ctx, uint64_t arena_offset, const void* src, uint64_t bytes);
 int seeml_b200_d2h(seeml_b200_ctx* ctx, uint64_t arena_offset, void* dst, uint64_t bytes);

@@ -20,6 +20,11 @@ class Scalars(C.Structure):
                 ("reserved", u32), ("step", u64)]
 
 
+class FusedGemm(C.Structure):
+    _fields_ = [(n, u64) for n in ("a_offset", "b_offset", "c_offset", "m", "n", "k", "a2_offset",
+                                   "b2_offset", "k2", "addend_offset")]
+
+
 class TrainReport(C.Structure):
     _fields_ = [("steps", u64), ("stopped_early", i32), ("initial_avg_loss", f32),
                 ("final_avg_loss", f32), ("has_validation", i32), ("val_initial_loss", f32),
@@ -55,6 +60,7 @@ SIGNATURES = {
     "seeml_b200_program_launches": (u64, [vp, INT]),
     "seeml_b200_program_run": (INT, [vp, INT, u64, u64, C.POINTER(Scalars)]),
     "seeml_b200_exec_one": (INT, [vp, vp, u32, C.POINTER(Scalars)]),
+    "seeml_b200_gemm_fused": (INT, [vp, C.POINTER(FusedGemm)]),
     "seeml_b200_h2d": (INT, [vp, u64, vp, u64]),
     "seeml_b200_d2h": (INT, [vp, u64, vp, u64]),
     "seeml_b200_memset": (INT, [vp, u64, INT, u64]),

@@ -45,7 +45,7 @@ def _stale(src, obj, deps):
 
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inc"))]
     headers.append(os.path.join(INCLUDE, "seeml_b200.h"))
     jobs = []
     objs = []

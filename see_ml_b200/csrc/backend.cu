@@ -6,6 +6,8 @@
 #include "backend.h"
 
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 namespace seeml_b200 {
@@ -326,6 +328,8 @@ int dispatch(Exec& x, const Instr& ins) {
   return 0;
 }
 
+#include "backend_fuse.inc"
+
 __global__ void set_scalars_kernel(DevScalars* dst, DevScalars v) { *dst = v; }
 
 int upload_scalars(seeml_b200_ctx* c, const seeml_b200_scalars* sc) {
@@ -424,7 +428,10 @@ void seeml_b200_ctx_destroy(seeml_b200_ctx* c) {
   cudaStreamSynchronize(c->stream);
   cudaStreamSynchronize(c->copy_stream);
   for (auto& p : c->programs)
-    if (p) for (auto& g : p->graphs) cudaGraphExecDestroy(g.second);
+    if (p) {
+      for (auto& g : p->graphs) cudaGraphExecDestroy(g.second);
+      for (auto& fs : p->steps) cudaFree(fs.bt);
+    }
   gemm_tensor_core_release(c);
   for (auto& kv : c->wt) cudaFree(kv.second);
   for (auto& kv : c->rope) cudaFree(kv.second);
@@ -474,6 +481,7 @@ int seeml_b200_program_build(seeml_b200_ctx* c, const void* instrs, uint64_t cou
     if (int r = prepare_instr(c, p->instrs[i], &loss_need, &ws_need)) return r;
   }
   if (int r = ensure_scratch(c, loss_need, ws_need)) return r;
+  if (int r = build_fused_steps(c, *p)) return r;
   c->programs.push_back(std::move(p));
   *program_id = static_cast<int>(c->programs.size()) - 1;
   return 0;
@@ -498,8 +506,20 @@ int seeml_b200_program_run(seeml_b200_ctx* c, int id, uint64_t begin, uint64_t e
   upload_scalars(c, scalars);
   Exec x{c};
   x.launches = 1;
-  for (uint64_t i = begin; i < end; ++i)
+  for (uint64_t i = begin; i < end;) {
+    const int32_t si = p.step_at.empty() ? -1 : p.step_at[i];
+    if (si >= 0 && i + p.steps[si].count <= end) {
+      const int fr = run_fused(x, p, p.steps[si]);
+      if (fr < 0) return 1;
+      if (fr == 1) { i += p.steps[si].count; continue; }
+      for (uint32_t q = 0; q < p.steps[si].count; ++q)
+        if (int r = dispatch(x, p.instrs[i + q])) return r;
+      i += p.steps[si].count;
+      continue;
+    }
     if (int r = dispatch(x, p.instrs[i])) return r;
+    ++i;
+  }
   p.last_launches = x.launches;
   if (c->timing) {
     CU(cudaEventRecord(c->t1, c->stream), "event record");
@@ -518,6 +538,55 @@ int seeml_b200_exec_one(seeml_b200_ctx* c, const void* instr, uint32_t version,
   if (!r) r = seeml_b200_sync(c);
   c->programs.pop_back();
   return r;
+}
+
+static int range_ok(seeml_b200_ctx* c, uint64_t off, uint64_t bytes);
+int seeml_b200_gemm_fused(seeml_b200_ctx* c, const seeml_b200_fused_gemm* f) {
+  if (!c || !f) return fail("UpdateEngine: null argument");
+  if (f->m == 0 || f->n == 0 || f->k == 0 || f->m > 0x7FFFFFFF || f->n > 0x7FFFFFFF || f->k > 0x7FFFFFFF ||
+      f->k2 > 0x7FFFFFFF)
+    return fail("UpdateEngine: fused GEMM dimension out of range");
+  const bool has_add = f->addend_offset != ~0ull;
+  if (range_ok(c, f->a_offset, f->m * f->k * 4) || range_ok(c, f->b_offset, f->n * f->k * 4) ||
+      range_ok(c, f->c_offset, f->m * f->n * 4) ||
+      (f->k2 && (range_ok(c, f->a2_offset, f->m * f->k2 * 4) || range_ok(c, f->b2_offset, f->n * f->k2 * 4))) ||
+      (has_add && range_ok(c, f->addend_offset, f->m * f->n * 4)))
+    return 1;
+  if ((f->a_offset | f->b_offset | f->c_offset | (f->k2 ? f->a2_offset | f->b2_offset : 0) |
+       (has_add ? f->addend_offset : 0)) & 3)
+    return fail("UpdateEngine: fused GEMM operand misaligned");
+  CU(cudaSetDevice(c->device), "cudaSetDevice");
+  auto at = [&](uint64_t off) { return reinterpret_cast<float*>(c->arena + off); };
+  uint64_t loss_need = 0, ws_need = 0;
+  Instr probe{};
+  probe.opcode = kGemmNT;
+  if (int r = gemm_tensor_core_prepare(c, probe)) return r;   // makes sure the tensor-core state exists
+  (void)loss_need; (void)ws_need;
+  TcGemm g{};
+  g.A = at(f->a_offset); g.Bt = at(f->b_offset); g.C = at(f->c_offset);
+  g.M = f->m; g.N = f->n; g.K = f->k;
+  if (f->k2) { g.A2 = at(f->a2_offset); g.B2t = at(f->b2_offset); g.K2 = f->k2; }
+  if (has_add) g.addend = at(f->addend_offset);
+  const int r = gemm_tc_launch(c, g);
+  if (r < 0) return 1;
+  if (r == 0) {
+    // CUDA-core form: the main product (plus addend), then the low-rank product accumulated on top
+    k::GemmDesc d = dense_desc(g.A, g.Bt, g.C, g.M, g.N, g.K);
+    d.sAm = (long long)g.K; d.sAk = 1; d.sBk = 1; d.sBn = (long long)g.K;
+    if (has_add) {
+      if (g.addend != g.C) CU(cudaMemcpyAsync(g.C, g.addend, g.M * g.N * 4, cudaMemcpyDeviceToDevice, c->stream), "addend");
+      d.accumulate = 1;
+    }
+    k::gemm_simt(d, nullptr, c->stream);
+    if (g.K2) {
+      k::GemmDesc e = dense_desc(g.A2, g.B2t, g.C, g.M, g.N, g.K2);
+      e.sAm = (long long)g.K2; e.sAk = 1; e.sBk = 1; e.sBn = (long long)g.K2;
+      e.accumulate = 1;
+      k::gemm_simt(e, nullptr, c->stream);
+    }
+  }
+  CU(cudaGetLastError(), "fused GEMM launch");
+  return 0;
 }
 
 static int range_ok(seeml_b200_ctx* c, uint64_t off, uint64_t bytes) {

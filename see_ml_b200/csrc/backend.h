@@ -22,6 +22,10 @@ int cuda_fail(cudaError_t e, const char* what);
 // Host-side validator (validate.cc): empty string = accepted.
 std::string validate_instruction(const Instr& ins, uint64_t arena_size, uint64_t rodata_size,
                                  uint32_t version);
+// The same proof, also returning the operand byte ranges it established (reads and writes).
+struct OpRange { uint64_t off, bytes; bool write, ro; };
+std::string validate_instruction_ranges(const Instr& ins, uint64_t arena_size, uint64_t rodata_size,
+                                        uint32_t version, std::vector<OpRange>* ranges_out);
 std::string verify_plan(const uint8_t* plan, uint64_t size, PlanHeader* header_out);
 uint64_t content_hash64(const uint8_t* p, uint64_t n);
 uint64_t plan_self_hash(const uint8_t* p, uint64_t n, uint64_t hash_off);
@@ -36,9 +40,32 @@ int gemm_tensor_core(seeml_b200_ctx* c, const Instr& ins, int* launches);
 int gemm_tensor_core_prepare(seeml_b200_ctx* c, const Instr& ins);
 void gemm_tensor_core_release(seeml_b200_ctx* c);
 int gemm_tensor_core_error(seeml_b200_ctx* c);
+// C[M,N] = (addend +) A[M,K].Bt[N,K]^T (+ A2[M,K2].B2t[N,K2]^T), then bias / activation.
+struct TcGemm {
+  const float* A; const float* Bt; float* C;
+  uint64_t M, N, K;
+  const float* A2; const float* B2t; uint64_t K2;
+  const float* addend; const float* bias; int act;
+};
+bool gemm_tc_shape_ok(const seeml_b200_ctx* c, uint64_t M, uint64_t N, uint64_t K);
+int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g);
+const float* gemm_tc_transposed_weight(seeml_b200_ctx* c, uint64_t rodata_off, uint64_t K, uint64_t N, bool create);
+
+// A group of consecutive instructions executed by fewer, fused kernels (FUSED mode).
+struct FusedStep {
+  enum Kind { kLoraFwd = 1, kLoraBwd = 2, kDgradAdd = 3, kSwigluFwd = 4, kSwigluBwd = 5 } kind;
+  uint32_t first = 0, count = 0;
+  uint32_t idx[8] = {0, 0, 0, 0, 0, 0, 0, 0};   // instruction indices of the group's members by role
+  float alpha = 1.0f;
+  float* bt = nullptr;                          // side buffer: alpha * B_lora^T, [N, r]
+  bool da_last = false;                         // dA after the dgrad GEMM (slot reuse, see backend_fuse.inc)
+  bool via_temp = false;                        // result lands in a dead slot first, then moves
+};
 
 struct Program {
   std::vector<Instr> instrs;
+  std::vector<FusedStep> steps;
+  std::vector<int32_t> step_at;                 // instruction index -> steps[] index, -1 = none
   uint32_t version = kSeeuVersion;
   uint32_t mode = SEEML_B200_MODE_CONTRACT;
   uint64_t last_launches = 0;

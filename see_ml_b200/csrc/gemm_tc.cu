@@ -137,9 +137,11 @@ __host__ __device__ constexpr uint32_t idesc_tf32(int m, int n) {
 
 struct TcParams {
   int M, N, K;
-  const float* bias;   // nullable, length N
-  int act;             // 0 none 1 relu 2 gelu 3 silu
-  int* err;            // device error word
+  int K2;                // reduction length of the optional second operand pair (0 = none)
+  const float* bias;     // nullable, length N
+  const float* addend;   // nullable, [M,N] row-major: C = addend + A.B^T (+ A2.B2^T)
+  int act;               // 0 none 1 relu 2 gelu 3 silu
+  int* err;              // device error word
 };
 
 __device__ __forceinline__ float epi_act(int act, float v) {
@@ -167,7 +169,8 @@ struct Smem {
 template <int BN, bool SPLIT, int STAGES>
 __global__ void __launch_bounds__(kThreadsTC, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-               const __grid_constant__ CUtensorMap mapC, TcParams p) {
+               const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapA2,
+               const __grid_constant__ CUtensorMap mapB2, TcParams p) {
   using S = Smem<BN, SPLIT, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -184,7 +187,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
-  const int nkb = (p.K + BK - 1) / BK;
+  // k-blocks of the main pair, then of the low-rank pair (C += A2[M,K2] . B2[N,K2]^T): the
+  // LoRA term rides the same accumulator as extra reduction steps
+  const int nkb1 = (p.K + BK - 1) / BK;
+  const int nkb = nkb1 + (p.K2 + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -215,8 +221,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         if (!ok) break;
         const uint32_t a_dst = base + s * S::kStageBytes, b_dst = a_dst + S::kABytes;
         mbar_expect_tx(bar_full(s), S::kRawBytes);
-        tma_load_2d(a_dst, &mapA, bar_full(s), kb * BK, m0);
-        tma_load_2d(b_dst, &mapB, bar_full(s), kb * BK, n0);
+        if (kb < nkb1) {
+          tma_load_2d(a_dst, &mapA, bar_full(s), kb * BK, m0);
+          tma_load_2d(b_dst, &mapB, bar_full(s), kb * BK, n0);
+        } else {
+          tma_load_2d(a_dst, &mapA2, bar_full(s), (kb - nkb1) * BK, m0);
+          tma_load_2d(b_dst, &mapB2, bar_full(s), (kb - nkb1) * BK, n0);
+        }
         ++issued;
       }
       if (!ok) {  // drain: let the copies already in flight land before the CTA retires
@@ -288,6 +299,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + c * 32, r);
         tmem_ld_wait();
+        if (p.addend != nullptr && m0 + row0 + lane < p.M) {
+          const float* arow = p.addend + (size_t)(m0 + row0 + lane) * p.N + ncol;
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            if (ncol + 4 * j4 < p.N) {          // N is a multiple of 4
+              const float4 d = *reinterpret_cast<const float4*>(arow + 4 * j4);
+              r[4 * j4 + 0] = __float_as_uint(d.x + __uint_as_float(r[4 * j4 + 0]));
+              r[4 * j4 + 1] = __float_as_uint(d.y + __uint_as_float(r[4 * j4 + 1]));
+              r[4 * j4 + 2] = __float_as_uint(d.z + __uint_as_float(r[4 * j4 + 2]));
+              r[4 * j4 + 3] = __float_as_uint(d.w + __uint_as_float(r[4 * j4 + 3]));
+            }
+          }
+        }
         if (p.bias != nullptr || p.act != 0) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -387,34 +411,21 @@ const CUtensorMap* cached_map(TcState& st, const void* ptr, uint64_t rows, uint6
   return &st.maps.emplace(key, m).first->second;
 }
 
-struct Shape {
-  bool ok = false;
-  bool need_transposed_b = false;
-  uint64_t M = 0, N = 0, K = 0;
-};
-// Which instructions take the tensor-core path: forward GEMMs through a frozen weight
-// (via its transposed copy) and A*B^T GEMMs, when the tile shapes and TMA alignment fit.
-Shape classify(const seeml_b200_ctx* c, const Instr& ins) {
-  Shape s;
-  if (c->gemm_kind == SEEML_B200_GEMM_FP32_SIMT || c->gemm_kind == SEEML_B200_GEMM_BF16) return s;
-  if (ins.opcode != kGemmNN && ins.opcode != kGemmNT) return s;
-  s.M = ins.out[0]; s.N = ins.out[1]; s.K = ins.out[2];
-  if (ins.opcode == kGemmNN) {
-    if (!is_rodata(ins.in[1])) return s;   // only frozen weights have a transposed copy
-    s.need_transposed_b = true;
-  }
-  if (s.M < 128 || s.N < 64 || s.K < 32) return s;
-  if (s.K % 4 != 0 || s.N % 4 != 0) return s;              // 16-byte global strides for TMA
-  if (s.M > 0x7FFFFFFF || s.N > 0x7FFFFFFF || s.K > 0x7FFFFFFF) return s;
-  if ((ref_off(ins.in[0]) | ref_off(ins.in[1]) | ref_off(ins.in[2])) & 15) return s;
-  if (2.0 * (double)s.M * (double)s.N * (double)s.K < 3.0e7) return s;   // too small to fill the machine
-  s.ok = true;
-  return s;
+}  // namespace
+
+bool gemm_tc_shape_ok(const seeml_b200_ctx* c, uint64_t M, uint64_t N, uint64_t K) {
+  if (c->gemm_kind == SEEML_B200_GEMM_FP32_SIMT || c->gemm_kind == SEEML_B200_GEMM_BF16) return false;
+  if (M < 128 || N < 64 || K < 32) return false;
+  if (K % 4 != 0 || N % 4 != 0) return false;              // 16-byte global strides for TMA
+  if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return false;
+  if (2.0 * (double)M * (double)N * (double)K < 3.0e7) return false;   // too small to fill the machine
+  return true;
 }
 
+namespace {
+
 template <int BN, bool SPLIT, int STAGES>
-int launch_tc(seeml_b200_ctx* c, TcState& st, const float* A, const float* Bt, float* C, const Shape& s,
-              const float* bias, int act) {
+int launch_tc(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   using S = Smem<BN, SPLIT, STAGES>;
   auto kern = gemm_tc_kernel<BN, SPLIT, STAGES>;
   static bool attr_done = false;
@@ -425,83 +436,118 @@ int launch_tc(seeml_b200_ctx* c, TcState& st, const float* A, const float* Bt, f
     }
     attr_done = true;
   }
-  const CUtensorMap* ma = cached_map(st, A, s.M, s.K, BM);
-  const CUtensorMap* mb = cached_map(st, Bt, s.N, s.K, BN);
-  const CUtensorMap* mc = cached_map(st, C, s.M, s.N, 32);
-  if (!ma || !mb || !mc) return -1;
-  TcParams p{(int)s.M, (int)s.N, (int)s.K, bias, act, st.err_dev};
-  dim3 grid((unsigned)((s.N + BN - 1) / BN), (unsigned)((s.M + BM - 1) / BM));
-  kern<<<grid, kThreadsTC, S::kTotal, c->stream>>>(*ma, *mb, *mc, p);
+  const CUtensorMap* ma = cached_map(st, g.A, g.M, g.K, BM);
+  const CUtensorMap* mb = cached_map(st, g.Bt, g.N, g.K, BN);
+  const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
+  const CUtensorMap* ma2 = g.K2 ? cached_map(st, g.A2, g.M, g.K2, BM) : ma;
+  const CUtensorMap* mb2 = g.K2 ? cached_map(st, g.B2t, g.N, g.K2, BN) : mb;
+  if (!ma || !mb || !mc || !ma2 || !mb2) return -1;
+  TcParams p{(int)g.M, (int)g.N, (int)g.K, (int)g.K2, g.bias, g.addend, g.act, st.err_dev};
+  dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((g.M + BM - 1) / BM));
+  kern<<<grid, kThreadsTC, S::kTotal, c->stream>>>(*ma, *mb, *mc, *ma2, *mb2, p);
   return 1;
+}
+
+TcState* state_of(seeml_b200_ctx* c, bool create) {
+  auto it = states().find(c);
+  if (it == states().end()) {
+    if (!create) return nullptr;
+    it = states().emplace(c, TcState{}).first;
+  }
+  TcState& st = it->second;
+  if (!st.err_dev && create) {
+    if (cudaMalloc(&st.err_dev, 64) != cudaSuccess) return nullptr;
+    cudaMemset(st.err_dev, 0, 64);
+  }
+  return &st;
 }
 
 }  // namespace
 
+// Launches C = (addend +) A.Bt^T (+ A2.B2t^T) on the tensor cores. 1 = launched, 0 = not
+// available for this context / shape (caller falls back), -1 = error.
+int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g) {
+  if (!gemm_tc_shape_ok(c, g.M, g.N, g.K)) return 0;
+  if (g.K2 && (g.K2 % 4 != 0)) return 0;
+  if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.Bt) | reinterpret_cast<uintptr_t>(g.C) |
+       reinterpret_cast<uintptr_t>(g.A2) | reinterpret_cast<uintptr_t>(g.B2t) |
+       reinterpret_cast<uintptr_t>(g.addend)) & 15)
+    return 0;
+  TcState* st = state_of(c, false);
+  if (!st || !st->usable || !st->err_dev) return 0;
+  const bool split = c->gemm_kind == SEEML_B200_GEMM_TF32X3;
+  int r;
+  if (g.N >= 192) r = split ? launch_tc<256, true, 2>(c, *st, g) : launch_tc<256, false, 4>(c, *st, g);
+  else r = split ? launch_tc<128, true, 3>(c, *st, g) : launch_tc<128, false, 6>(c, *st, g);
+  if (r < 0) {   // tensor maps / attributes unavailable: leave the CUDA-core path in charge
+    st->usable = false;
+    return 0;
+  }
+  return 1;
+}
+
+// Transposed [N,K] copy of the frozen weight at `rodata_off` ([K,N]); made on first request.
+const float* gemm_tc_transposed_weight(seeml_b200_ctx* c, uint64_t rodata_off, uint64_t K, uint64_t N, bool create) {
+  const auto key = std::make_tuple(rodata_off, K, N);
+  auto it = c->wt.find(key);
+  if (it != c->wt.end()) return it->second;
+  if (!create) return nullptr;
+  float* t = nullptr;
+  if (cudaMalloc(&t, K * N * sizeof(float)) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  const float* w = reinterpret_cast<const float*>(c->rodata + rodata_off);
+  dim3 grid((unsigned)((N + 31) / 32), (unsigned)((K + 31) / 32)), block(32, 8);
+  transpose_kernel<<<grid, block, 0, c->stream>>>(w, t, (int)K, (int)N);
+  c->wt[key] = t;
+  return t;
+}
+
+static bool tc_instr(const seeml_b200_ctx* c, const Instr& ins) {
+  if (ins.opcode != kGemmNN && ins.opcode != kGemmNT) return false;
+  if (ins.opcode == kGemmNN && !is_rodata(ins.in[1])) return false;   // only frozen weights have a transposed copy
+  return gemm_tc_shape_ok(c, ins.out[0], ins.out[1], ins.out[2]);
+}
+
 int gemm_tensor_core_prepare(seeml_b200_ctx* c, const Instr& ins) {
-  const Shape s = classify(c, ins);
-  if (!s.ok) return 0;
-  TcState& st = states()[c];
-  if (!st.err_dev) {
-    if (cudaMalloc(&st.err_dev, 64) != cudaSuccess) return cuda_fail(cudaGetLastError(), "tc error word");
-    cudaMemset(st.err_dev, 0, 64);
-  }
-  if (s.need_transposed_b) {
-    const auto key = std::make_tuple(ref_off(ins.in[1]), s.K, s.N);
-    if (!c->wt.count(key)) {
-      float* t = nullptr;
-      if (cudaMalloc(&t, s.K * s.N * sizeof(float)) != cudaSuccess)
-        return cuda_fail(cudaGetLastError(), "transposed weight alloc");
-      const float* w = reinterpret_cast<const float*>(c->rodata + ref_off(ins.in[1]));
-      dim3 grid((unsigned)((s.N + 31) / 32), (unsigned)((s.K + 31) / 32)), block(32, 8);
-      transpose_kernel<<<grid, block, 0, c->stream>>>(w, t, (int)s.K, (int)s.N);
-      c->wt[key] = t;
-    }
-  }
+  if (c->gemm_kind == SEEML_B200_GEMM_FP32_SIMT || c->gemm_kind == SEEML_B200_GEMM_BF16) return 0;
+  if (!state_of(c, true)) return cuda_fail(cudaGetLastError(), "tc error word");
+  if (!tc_instr(c, ins)) return 0;
+  if (ins.opcode == kGemmNN &&
+      !gemm_tc_transposed_weight(c, ref_off(ins.in[1]), ins.out[2], ins.out[1], true))
+    return fail("UpdateEngine: transposed weight allocation failed");
   return 0;
 }
 
 int gemm_tensor_core(seeml_b200_ctx* c, const Instr& ins, int* launches) {
-  const Shape s = classify(c, ins);
-  if (!s.ok) return 0;
-  auto sit = states().find(c);
-  if (sit == states().end() || !sit->second.usable || !sit->second.err_dev) return 0;
-  TcState& st = sit->second;
-  const float* A = reinterpret_cast<const float*>((is_rodata(ins.in[0]) ? c->rodata : c->arena) + ref_off(ins.in[0]));
-  const float* B;
-  if (s.need_transposed_b) {
-    auto it = c->wt.find(std::make_tuple(ref_off(ins.in[1]), s.K, s.N));
-    if (it == c->wt.end()) return 0;
-    B = it->second;
-  } else {
-    B = reinterpret_cast<const float*>((is_rodata(ins.in[1]) ? c->rodata : c->arena) + ref_off(ins.in[1]));
-  }
-  float* C = reinterpret_cast<float*>(c->arena + ref_off(ins.in[2]));
-  const float* bias = nullptr;
-  int act = 0;
+  if (!tc_instr(c, ins)) return 0;
+  auto at = [&](uint64_t ref) {
+    return reinterpret_cast<const float*>((is_rodata(ref) ? c->rodata : c->arena) + ref_off(ref));
+  };
+  TcGemm g{};
+  g.A = at(ins.in[0]);
+  g.M = ins.out[0]; g.N = ins.out[1]; g.K = ins.out[2];
   if (ins.opcode == kGemmNN) {
-    if (ins.flags & kFlagBias) bias = reinterpret_cast<const float*>((is_rodata(ins.in[3]) ? c->rodata : c->arena) + ref_off(ins.in[3]));
-    act = (ins.flags & kFlagActMask) >> kFlagActShift;
+    g.Bt = gemm_tc_transposed_weight(c, ref_off(ins.in[1]), g.K, g.N, false);
+    if (!g.Bt) return 0;
+    if (ins.flags & kFlagBias) g.bias = at(ins.in[3]);
+    g.act = (ins.flags & kFlagActMask) >> kFlagActShift;
+  } else {
+    g.Bt = at(ins.in[1]);
   }
-  const bool split = c->gemm_kind == SEEML_B200_GEMM_TF32X3;
-  int r;
-  if (s.N >= 192) r = split ? launch_tc<256, true, 2>(c, st, A, B, C, s, bias, act)
-                            : launch_tc<256, false, 4>(c, st, A, B, C, s, bias, act);
-  else r = split ? launch_tc<128, true, 3>(c, st, A, B, C, s, bias, act)
-                 : launch_tc<128, false, 6>(c, st, A, B, C, s, bias, act);
-  if (r < 0) {           // tensor maps / attributes unavailable: leave the CUDA-core path in charge
-    st.usable = false;
-    return 0;
-  }
-  *launches = 1;
-  return 1;
+  g.C = reinterpret_cast<float*>(c->arena + ref_off(ins.in[2]));
+  const int r = gemm_tc_launch(c, g);
+  if (r == 1) *launches = 1;
+  return r;
 }
 
 // Nonzero when a tensor-core kernel of this context gave up on a bounded wait.
 int gemm_tensor_core_error(seeml_b200_ctx* c) {
-  auto sit = states().find(c);
-  if (sit == states().end() || !sit->second.err_dev) return 0;
+  TcState* st = state_of(c, false);
+  if (!st || !st->err_dev) return 0;
   int v = 0;
-  cudaMemcpyAsync(&v, sit->second.err_dev, 4, cudaMemcpyDeviceToHost, c->stream);
+  cudaMemcpyAsync(&v, st->err_dev, 4, cudaMemcpyDeviceToHost, c->stream);
   cudaStreamSynchronize(c->stream);
   return v;
 }

@@ -100,6 +100,11 @@ uint64_t plan_self_hash(const uint8_t* p, uint64_t n, uint64_t hash_off) {
 // spaces and aliasing. Reference: runtime/validator/plan_validator.cc:9-343.
 std::string validate_instruction(const Instr& ins, uint64_t arena_size, uint64_t rodata_size,
                                  uint32_t version) {
+  return validate_instruction_ranges(ins, arena_size, rodata_size, version, nullptr);
+}
+
+std::string validate_instruction_ranges(const Instr& ins, uint64_t arena_size, uint64_t rodata_size,
+                                        uint32_t version, std::vector<OpRange>* ranges_out) {
   const std::string opc = std::to_string(ins.opcode);
   if (version < kFlagsVersion) {
     if (ins.flags != 0)
@@ -303,6 +308,10 @@ std::string validate_instruction(const Instr& ins, uint64_t arena_size, uint64_t
       if (a.off < b.off + b.bytes && b.off < a.off + a.bytes)
         return "PlanValidator: instruction operands alias a written range (opcode " + opc + ")";
     }
+  if (ranges_out) {
+    ranges_out->clear();
+    for (int i = 0; i < nr; ++i) ranges_out->push_back({rg[i].off, rg[i].bytes, rg[i].write, rg[i].ro});
+  }
   return {};
 }
 

@@ -252,3 +252,55 @@ def test_dataset_contract_violations_are_refused(golden_dir):
         m.load_from_memory(bytes(blob))
     pc = next(p for p in plancases.plan_cases() if p.name == "mlp_tiny")
     assert m.train(pc.dataset(), 2).steps == 2
+
+
+def test_fused_groups_match_contract_mode_and_oracle_on_tensor_core_shapes():
+    """A decoder wide enough for the tensor-core GEMM and the LoRA group fusions (forward
+    C' = [X|t].[W^T|aB^T]^T, backward dX = [p+][g|dt].[W|A]^T, rank-r kernels): every LoRA
+    gradient and the loss after one hand-fed backward pass, fused vs one-kernel-per-
+    instruction vs the C oracle. Adapters' B factors are made nonzero so every path carries
+    signal."""
+    from see_ml_b200 import plansynth as PS
+    from see_ml_b200.engine import UpdateEngine
+    lib = L.lib()
+    rng = np.random.default_rng(11)
+    V, D, H, Ff, S, T = 512, 256, 4, 512, 64, 512
+    model = PS.llama_decoder(V, D, H, Ff, 2, S, rng, std=0.05)
+    spec = PS.TrainSpec(batch=T, lora_rank=8, lora_alpha=16.0,
+                        targets=("wq", "wk", "wv", "wo", "w_up", "w_down"))
+    blob, info = PS.synthesize(model, spec, hasher=lambda b, o: int(
+        lib.seeml_b200_plan_self_hash(np.frombuffer(b, np.uint8).ctypes.data, len(b), o)))
+    plan = F.parse_plan(blob)
+    h = plan.header
+    recs = rng.integers(0, V, (T // S, S + 1)).astype(np.int32)
+    tok, lab = recs[:, :-1].reshape(-1).copy(), recs[:, 1:].reshape(-1).copy()
+    bvals = {ad["b_ref"]: (rng.standard_normal(ad["r"] * ad["m"]) * 0.05).astype(np.float32)
+             for ad in info.adapters}
+    opt_begin = int(np.nonzero(plan.train["opcode"] == int(F.Op.ADAMW))[0][0])
+    want = np.zeros(F.align_up(h.arena_size), np.uint8)
+    want[:h.persist_init_size] = plan.persist_init
+    for ref, v in bvals.items():
+        want[ref:ref + v.nbytes] = v.view(np.uint8)
+    want[h.input_ref:h.input_ref + tok.nbytes] = tok.view(np.uint8)
+    want[h.label_ref:h.label_ref + lab.nbytes] = lab.view(np.uint8)
+    O.execute("port", plan.train[:opt_begin], want, np.asarray(plan.rodata))
+    results = {}
+    for mode in (0, 1):
+        e = UpdateEngine(0, mode, 0)
+        e.load_from_memory(blob)
+        for ref, v in bvals.items():
+            e.arena_write(ref, v)
+        e.arena_write(h.input_ref, tok)
+        e.arena_write(h.label_ref, lab)
+        e.run_train_range(0, e.opt_begin())
+        results[mode] = (e.loss_value(), {pid: e.arena_read(g, n * 4).view(np.float32) for pid, _, g, n in info.params},
+                         e.last_launches())
+        e.close()
+    assert results[1][2] < results[0][2], "fused mode launched no fewer kernels: nothing was fused"
+    wl = float(want[h.loss_ref:h.loss_ref + 4].view(np.float32)[0])
+    for mode in (0, 1):
+        assert abs(results[mode][0] - wl) <= 1e-4 * abs(wl)
+        for pid, _, g, n in info.params:
+            ref = want[g:g + n * 4].view(np.float32)
+            np.testing.assert_allclose(results[mode][1][pid], ref, rtol=1e-3, atol=1e-4 * max(1.0, np.abs(ref).max()),
+                                       err_msg=f"mode {mode} {pid}")
