@@ -174,6 +174,40 @@ uint64_t scratch_need_loss(const Instr& ins) {
   }
 }
 
+// The six per-head products of attention on the tensor cores (0 when the shape is not
+// eligible and the CUDA-core descriptors below run instead). which: 0 scores = alpha Q K^T
+// (masked), 1 O = P V, 2 dP = dO V^T (masked), 3 dV/dK = alpha X^T Y (X = P or dS), 4 dQ =
+// alpha dS K. Q/K/V/O-like operands are [B*S, H*dh]; P-like operands are [B*H*S, S].
+static int attn_tc(seeml_b200_ctx* c, int which, const float* A, const float* Bm, float* C, uint64_t B, uint64_t S,
+                   uint64_t H, uint64_t dh, float alpha) {
+  if (S % 128 != 0 || dh % 64 != 0) return 0;
+  const uint64_t T = B * S, D = H * dh;
+  TcBatched g{};
+  g.A = A; g.B = Bm; g.C = C;
+  g.batch = (int)(B * H); g.H = (int)H; g.alpha = alpha;
+  auto seq = [&](uint64_t& rows, uint64_t& cols, int* x, int* y) {   // [T, D] operand
+    rows = T; cols = D; x[0] = 0; x[1] = (int)dh; y[0] = (int)S; y[1] = 0;
+  };
+  auto sq = [&](uint64_t& rows, uint64_t& cols, int* x, int* y) {    // [B*H*S, S] operand
+    rows = B * H * S; cols = S; x[0] = 0; x[1] = 0; y[0] = (int)(H * S); y[1] = (int)S;
+  };
+  switch (which) {
+    case 0: case 2:
+      seq(g.a_rows, g.a_cols, g.ax, g.ay); seq(g.b_rows, g.b_cols, g.bx, g.by); sq(g.c_rows, g.c_cols, g.cx, g.cy);
+      g.M = (int)S; g.N = (int)S; g.K = (int)dh; g.causal = 1;
+      break;
+    case 1: case 4:
+      sq(g.a_rows, g.a_cols, g.ax, g.ay); seq(g.b_rows, g.b_cols, g.bx, g.by); seq(g.c_rows, g.c_cols, g.cx, g.cy);
+      g.b_t = true; g.M = (int)S; g.N = (int)dh; g.K = (int)S; g.causal = 2;
+      break;
+    default:
+      sq(g.a_rows, g.a_cols, g.ax, g.ay); seq(g.b_rows, g.b_cols, g.bx, g.by); seq(g.c_rows, g.c_cols, g.cx, g.cy);
+      g.a_t = true; g.b_t = true; g.M = (int)S; g.N = (int)dh; g.K = (int)S; g.causal = 3;
+      break;
+  }
+  return gemm_tc_batched(c, g);
+}
+
 int dispatch(Exec& x, const Instr& ins) {
   seeml_b200_ctx* c = x.c;
   cudaStream_t st = c->stream;
@@ -243,7 +277,8 @@ int dispatch(Exec& x, const Instr& ins) {
       s.sCb0 = (long long)(H * S * S); s.sCb1 = (long long)(S * S);
       s.alpha = 1.0f / std::sqrt(static_cast<float>(dh));
       s.causal = 1;
-      n += k::gemm_simt(s, nullptr, st);
+      if (attn_tc(c, 0, s.A, s.B, P, B, S, H, dh, s.alpha) == 1) n += 1;
+      else n += k::gemm_simt(s, nullptr, st);
       n += k::causal_softmax_rows(P, B * H, S, st);
       k::GemmDesc pv = attn_desc(B, S, H, dh);
       pv.A = P; pv.B = x.R(in[2]); pv.C = x.W(in[3]);
@@ -252,7 +287,8 @@ int dispatch(Exec& x, const Instr& ins) {
       pv.sAb0 = s.sCb0; pv.sAb1 = s.sCb1; pv.sBb0 = s.sAb0; pv.sBb1 = s.sAb1;
       pv.sCb0 = s.sAb0; pv.sCb1 = s.sAb1;
       pv.causal = 2;
-      n += k::gemm_simt(pv, nullptr, st);
+      if (attn_tc(c, 1, P, pv.B, pv.C, B, S, H, dh, 1.0f) == 1) n += 1;
+      else n += k::gemm_simt(pv, nullptr, st);
       break;
     }
     case kAttnDP: {  // dP = dO V^T, masked entries zero
@@ -265,7 +301,8 @@ int dispatch(Exec& x, const Instr& ins) {
       s.sAb0 = (long long)S * D; s.sAb1 = (long long)dh; s.sBb0 = s.sAb0; s.sBb1 = s.sAb1;
       s.sCb0 = (long long)(H * S * S); s.sCb1 = (long long)(S * S);
       s.causal = 1;
-      n = k::gemm_simt(s, nullptr, st);
+      if (attn_tc(c, 2, s.A, s.B, s.C, B, S, H, dh, 1.0f) == 1) n = 1;
+      else n = k::gemm_simt(s, nullptr, st);
       break;
     }
     case kAttnDV: case kAttnDK: {  // dV = P^T dO ; dK = dS^T Q / sqrt(d)
@@ -280,7 +317,8 @@ int dispatch(Exec& x, const Instr& ins) {
       g.sBb0 = (long long)S * D; g.sBb1 = (long long)dh; g.sCb0 = g.sBb0; g.sCb1 = g.sBb1;
       g.causal = 3;
       if (ins.opcode == kAttnDK) g.alpha = 1.0f / std::sqrt(static_cast<float>(dh));
-      n = k::gemm_simt(g, nullptr, st);
+      if (attn_tc(c, 3, g.A, g.B, g.C, B, S, H, dh, g.alpha) == 1) n = 1;
+      else n = k::gemm_simt(g, nullptr, st);
       break;
     }
     case kAttnDQ: {  // dQ = dS K / sqrt(d)
@@ -294,7 +332,8 @@ int dispatch(Exec& x, const Instr& ins) {
       g.sBb0 = (long long)S * D; g.sBb1 = (long long)dh; g.sCb0 = g.sBb0; g.sCb1 = g.sBb1;
       g.causal = 2;
       g.alpha = 1.0f / std::sqrt(static_cast<float>(dh));
-      n = k::gemm_simt(g, nullptr, st);
+      if (attn_tc(c, 4, g.A, g.B, g.C, B, S, H, dh, g.alpha) == 1) n = 1;
+      else n = k::gemm_simt(g, nullptr, st);
       break;
     }
     case kSoftmaxRowsBwd:

@@ -48,6 +48,19 @@ struct TcGemm {
   const float* addend; const float* bias; int act;
 };
 bool gemm_tc_shape_ok(const seeml_b200_ctx* c, uint64_t M, uint64_t N, uint64_t K);
+// Batched per-head product C_z = alpha * A_z . B_z (z = b * H + h); every operand is a window
+// of a 2-D row-major f32 matrix whose origin for item z is (x, y) = (b*?x[0] + h*?x[1],
+// b*?y[0] + h*?y[1]) in (column, row) coordinates. a_t: A stored [K,M]; b_t: B stored [K,N]
+// (otherwise [M,K] and [N,K]). causal as in the CUDA-core GEMM descriptor (0..3).
+struct TcBatched {
+  const float* A; const float* B; float* C;
+  uint64_t a_rows, a_cols, b_rows, b_cols, c_rows, c_cols;
+  bool a_t, b_t;
+  int ax[2], ay[2], bx[2], by[2], cx[2], cy[2];
+  int M, N, K, batch, H, causal;
+  float alpha;
+};
+int gemm_tc_batched(seeml_b200_ctx* c, const TcBatched& g);
 int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g);
 const float* gemm_tc_transposed_weight(seeml_b200_ctx* c, uint64_t rodata_off, uint64_t K, uint64_t N, bool create);
 

@@ -12,8 +12,9 @@
 // shared memory from the TMA-loaded f32 tiles, so no extra global traffic is spent
 // on the split. TF32 is the single-product mode.
 //
-// Warp roles (192 threads): warp 0 issues TMA loads, warp 1 owns TMEM and issues the
-// MMAs, warps 2..5 split the operands during the main loop and run the epilogue.
+// Warp roles (320 threads): warp 0 issues TMA loads, warp 1 owns TMEM and issues the
+// MMAs, warps 2..9 split the operands, collect finished accumulation chunks into registers
+// and run the epilogue (the batched attention kernel keeps 4 such warps).
 // Every wait on an mbarrier is bounded: on expiry the kernel records an error code,
 // drains, frees its TMEM and returns, so a protocol bug cannot hang the device.
 //
@@ -25,115 +26,16 @@
 #include <cstring>
 
 #include "backend.h"
+#include "tc_ptx.cuh"
 
 namespace seeml_b200 {
 namespace {
 
+using namespace tc;
+
 constexpr int BM = 128;
 constexpr int BK = 32;                 // f32 elements = one 128-byte swizzle row
 constexpr int kThreadsTC = 192;
-constexpr uint32_t kSpinLimit = 1u << 21;
-
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false (and an error code left in *err) when the phase never completes.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i)
-    if (mbar_try(bar, parity)) return true;
-  atomicCAS(err, 0, code);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(map), "r"(src), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(addr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory operand descriptor: K-major tile whose rows are one 128-byte swizzle
-// atom wide; 8-row groups are 1024 bytes apart. Fields (bit positions): start address
-// >>4 [0,14), leading byte offset >>4 [16,30) (unused for swizzled K-major, 1),
-// stride byte offset >>4 [32,46) = 64, descriptor version [46,48) = 1 on sm_100,
-// layout type [61,64) = 2 (128-byte swizzle).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  uint64_t d = (uint64_t)((addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-// Instruction descriptor, kind::tf32: D = f32 [4,6)=1, A = B = tf32 [7,10)=[10,13)=2,
-// both operands K-major (bits 15, 16 = 0), N>>3 at [17,23), M>>4 at [24,29).
-__host__ __device__ constexpr uint32_t idesc_tf32(int m, int n) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
 
 struct TcParams {
   int M, N, K;
@@ -155,19 +57,29 @@ __device__ __forceinline__ float epi_act(int act, float v) {
 }
 
 // ------------------------------------------------------------------- the kernel
+// The tensor core adds into its f32 accumulator with truncation, so a long reduction kept
+// in TMEM alone drifts (error ~ steps * 2^-24 * |partial sum|). The reduction is therefore
+// cut into chunks of kChunk k-blocks that alternate between two TMEM accumulators; the worker
+// warps add every finished chunk into f32 registers (round-to-nearest) while the next chunk is
+// being multiplied, and the output tile is stored from those registers.
+constexpr int kChunk = 4;              // k-blocks (x 32 elements) per TMEM accumulation chunk
+constexpr int kWorkers = 256;          // threads of the 8 split / accumulate / epilogue warps
+constexpr int kThreadsV2 = 64 + kWorkers;
+
 template <int BN, bool SPLIT, int STAGES>
 struct Smem {
   static constexpr int kABytes = BM * BK * 4;             // 16 KiB
   static constexpr int kBBytes = BN * BK * 4;
   static constexpr int kRawBytes = kABytes + kBBytes;
   static constexpr int kStageBytes = kRawBytes * (SPLIT ? 2 : 1);
-  static constexpr int kEpiBytes = 4 * 32 * 128;          // one 32x32 f32 box per epilogue warp
+  static constexpr int kEpiBytes = 8 * 32 * 128;          // one 32x32 f32 box per worker warp (aliases stage 0)
   static constexpr int kBarBytes = 256;
-  static constexpr int kTotal = STAGES * kStageBytes + kEpiBytes + kBarBytes + 1024;  // + alignment slack
+  static constexpr int kTotal = STAGES * kStageBytes + kBarBytes + 1024;  // + alignment slack
+  static_assert(STAGES * kStageBytes >= kEpiBytes, "store staging must fit in the stage buffers");
 };
 
 template <int BN, bool SPLIT, int STAGES>
-__global__ void __launch_bounds__(kThreadsTC, 1)
+__global__ void __launch_bounds__(kThreadsV2, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapA2,
                const __grid_constant__ CUtensorMap mapB2, TcParams p) {
@@ -175,34 +87,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t epi = base + STAGES * S::kStageBytes;
-  const uint32_t bars = epi + S::kEpiBytes;
+  const uint32_t bars = base + STAGES * S::kStageBytes;
   auto bar_full = [&](int s) { return bars + 8u * s; };
   auto bar_split = [&](int s) { return bars + 8u * (STAGES + s); };
   auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
-  const uint32_t bar_accum = bars + 8u * (3 * STAGES);
-  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 1);
+  auto bar_acc_full = [&](int b) { return bars + 8u * (3 * STAGES + b); };
+  auto bar_acc_empty = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 4);
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStageBytes + S::kEpiBytes + 8 * (3 * STAGES + 1));
+      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStageBytes + 8 * (3 * STAGES + 4));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   // k-blocks of the main pair, then of the low-rank pair (C += A2[M,K2] . B2[N,K2]^T): the
-  // LoRA term rides the same accumulator as extra reduction steps
+  // LoRA term rides the same accumulators as extra reduction steps
   const int nkb1 = (p.K + BK - 1) / BK;
   const int nkb = nkb1 + (p.K2 + BK - 1) / BK;
+  const int nchunks = (nkb + kChunk - 1) / kChunk;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full(s), 1);
-      mbar_init(bar_split(s), 128);
+      mbar_init(bar_split(s), kWorkers);
       mbar_init(bar_empty(s), 1);
     }
-    mbar_init(bar_accum, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), kWorkers);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, BN);
+    tmem_alloc(tmem_slot, 2 * BN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -242,38 +158,69 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       bool ok = true;
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % STAGES, r = kb / STAGES;
+        const int ci = kb / kChunk, buf = ci & 1;
+        if (kb % kChunk == 0 && ci >= 2) {      // the accumulator's previous chunk must have been collected
+          ok = mbar_wait(bar_acc_empty(buf), ((ci >> 1) - 1) & 1, p.err, 6);
+          if (!ok) break;
+          tc_fence_after();
+        }
         ok = mbar_wait(SPLIT ? bar_split(s) : bar_full(s), r & 1, p.err, 2);
         if (!ok) break;
         tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
         const uint32_t a_raw = base + s * S::kStageBytes, b_raw = a_raw + S::kABytes;
         const uint32_t a_lo = a_raw + S::kRawBytes, b_lo = b_raw + S::kRawBytes;
 #pragma unroll
         for (int kk = 0; kk < BK / 8; ++kk) {
           const uint64_t da = smem_desc_sw128(a_raw + kk * 32), db = smem_desc_sw128(b_raw + kk * 32);
-          mma_tf32(tmem_base, da, db, idesc, (kb | kk) != 0);
+          mma_tf32(tmem_d, da, db, idesc, ((kb % kChunk) | kk) != 0);
           if (SPLIT) {
-            mma_tf32(tmem_base, smem_desc_sw128(a_lo + kk * 32), db, idesc, 1);
-            mma_tf32(tmem_base, da, smem_desc_sw128(b_lo + kk * 32), idesc, 1);
+            mma_tf32(tmem_d, smem_desc_sw128(a_lo + kk * 32), db, idesc, 1);
+            mma_tf32(tmem_d, da, smem_desc_sw128(b_lo + kk * 32), idesc, 1);
           }
         }
         mma_commit(bar_empty(s));
+        if (kb % kChunk == kChunk - 1 || kb == nkb - 1) mma_commit(bar_acc_full(buf));
       }
-      if (ok) mma_commit(bar_accum);
     }
   } else {
-    // ---- split warps, then epilogue -----------------------------------------------------
+    // ---- worker warps: split, collect finished chunks, epilogue ---------------------------
     const int t = threadIdx.x - 64;
+    const int q = warp & 3;                     // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;           // which half of the tile's columns it owns
+    const int row0 = q * 32;
+    constexpr int NH = BN / 2;
+    float acc[NH];
+#pragma unroll
+    for (int j = 0; j < NH; ++j) acc[j] = 0.0f;
     bool ok = true;
-    if (SPLIT) {
-      constexpr int NV = S::kRawBytes / 16;
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        const int s = kb % STAGES, r = kb / STAGES;
+    int collected = 0;
+    auto collect = [&](int ci) {
+      const int buf = ci & 1;
+      if (!mbar_wait(bar_acc_full(buf), (ci >> 1) & 1, p.err, 4)) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < NH / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + buf * BN + half * NH + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[c * 32 + j] += __uint_as_float(r[j]);
+      }
+      tc_fence_before();
+      mbar_arrive(bar_acc_empty(buf));
+      return true;
+    };
+    for (int kb = 0; kb < nkb && ok; ++kb) {
+      const int s = kb % STAGES, r = kb / STAGES;
+      if (SPLIT) {
+        constexpr int NV = S::kRawBytes / 16;
         ok = mbar_wait(bar_full(s), r & 1, p.err, 3);
         if (!ok) break;
         const float4* raw = reinterpret_cast<const float4*>(base_ptr + s * S::kStageBytes);
         float4* lo = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes + S::kRawBytes);
 #pragma unroll 4
-        for (int i = t; i < NV; i += 128) {
+        for (int i = t; i < NV; i += kWorkers) {
           const float4 v = raw[i];
           float4 l;
           l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
@@ -285,46 +232,270 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         fence_async_smem();
         mbar_arrive(bar_split(s));
       }
+      // one k-block into chunk ci the previous chunk has been multiplied: collect it now, while
+      // the tensor core works on the blocks already split
+      if (kb % kChunk == 1 && kb > kChunk) {
+        ok = collect(collected);
+        ++collected;
+      }
     }
-    if (ok) ok = mbar_wait(bar_accum, 0, p.err, 4);
-    tc_fence_after();
-    const int q = warp & 3;                     // TMEM lane quadrant this warp may read
-    const int row0 = q * 32;
+    for (; ok && collected < nchunks; ++collected) ok = collect(collected);
     if (ok && m0 + row0 < p.M) {
-      const uint32_t stage = epi + q * 4096;
-      uint8_t* stage_ptr = base_ptr + STAGES * S::kStageBytes + q * 4096;
-      for (int c = 0; c < BN / 32; ++c) {
-        const int ncol = n0 + c * 32;
-        if (ncol >= p.N) break;
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + c * 32, r);
-        tmem_ld_wait();
-        if (p.addend != nullptr && m0 + row0 + lane < p.M) {
-          const float* arow = p.addend + (size_t)(m0 + row0 + lane) * p.N + ncol;
+      // every product has retired (the last chunk was collected): stage 0 serves as store staging
+      const uint32_t stage = base + (warp - 2) * 4096;
+      uint8_t* stage_ptr = base_ptr + (warp - 2) * 4096;
 #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            if (ncol + 4 * j4 < p.N) {          // N is a multiple of 4
-              const float4 d = *reinterpret_cast<const float4*>(arow + 4 * j4);
-              r[4 * j4 + 0] = __float_as_uint(d.x + __uint_as_float(r[4 * j4 + 0]));
-              r[4 * j4 + 1] = __float_as_uint(d.y + __uint_as_float(r[4 * j4 + 1]));
-              r[4 * j4 + 2] = __float_as_uint(d.z + __uint_as_float(r[4 * j4 + 2]));
-              r[4 * j4 + 3] = __float_as_uint(d.w + __uint_as_float(r[4 * j4 + 3]));
+      for (int c = 0; c < NH / 32; ++c) {
+        const int ncol = n0 + half * NH + c * 32;
+        if (ncol < p.N) {
+          uint32_t r[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(acc[c * 32 + j]);
+          if (p.addend != nullptr && m0 + row0 + lane < p.M) {
+            const float* arow = p.addend + (size_t)(m0 + row0 + lane) * p.N + ncol;
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+              if (ncol + 4 * j4 < p.N) {          // N is a multiple of 4
+                const float4 d = *reinterpret_cast<const float4*>(arow + 4 * j4);
+                r[4 * j4 + 0] = __float_as_uint(d.x + __uint_as_float(r[4 * j4 + 0]));
+                r[4 * j4 + 1] = __float_as_uint(d.y + __uint_as_float(r[4 * j4 + 1]));
+                r[4 * j4 + 2] = __float_as_uint(d.z + __uint_as_float(r[4 * j4 + 2]));
+                r[4 * j4 + 3] = __float_as_uint(d.w + __uint_as_float(r[4 * j4 + 3]));
+              }
             }
           }
-        }
-        if (p.bias != nullptr || p.act != 0) {
+          if (p.bias != nullptr || p.act != 0) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float v = __uint_as_float(r[j]);
-            if (p.bias != nullptr && ncol + j < p.N) v = v + p.bias[ncol + j];
-            r[j] = __float_as_uint(epi_act(p.act, v));
+            for (int j = 0; j < 32; ++j) {
+              float v = __uint_as_float(r[j]);
+              if (p.bias != nullptr && ncol + j < p.N) v = v + p.bias[ncol + j];
+              r[j] = __float_as_uint(epi_act(p.act, v));
+            }
+          }
+          if (c > 0) {
+            if (lane == 0) tma_store_wait_read();   // the staging box of the previous chunk is free
+            __syncwarp();
+          }
+          // row = lane; 16-byte chunk j lands at (j ^ (row & 7)): the 128-byte swizzle the store expects
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 v = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            *reinterpret_cast<uint4*>(stage_ptr + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&mapC, stage, ncol, m0 + row0);
+            tma_store_commit();
           }
         }
+      }
+      if (lane == 0) tma_store_wait_all();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+}
+
+// ------------------------------------------------- batched per-head products (attention)
+// C_z[M,N] = alpha * A_z[M,K] . B_z[K,N] for z = b * H + h, every operand a window of a 2-D
+// row-major matrix addressed through TMA coordinates (x0 = b*xb + h*xh, y0 = b*yb + h*yh).
+// An operand may be stored "transposed" for the tensor core (A as [K,M], B as [K,N], the
+// reduction index on rows): its tile is loaded unswizzled and the split warps write the hi
+// and lo tiles K-major with the 128-byte swizzle while they split it, so no transposed copy
+// of P, dS or V ever goes through global memory. Causal structure: mode 1 masks outputs with
+// n > m (tiles wholly above the diagonal skip the products and store zeros), mode 2 stops the
+// reduction at the tile's last row (A[m,k] = 0 for k > m), mode 3 starts it at the tile's
+// first row (A[m,k] = 0 for k < m). M % 128 == 0, N % BN == 0 and K % 32 == 0 are required
+// (windows of neighbouring heads touch, so the TMA cannot clip ragged edges here).
+struct BgParams {
+  int nkb;                 // K / 32
+  int causal;
+  float alpha;
+  int H;
+  int ax[2], ay[2], bx[2], by[2], cx[2], cy[2];
+  int x3;                  // three products (f32-class accuracy) or one
+  int* err;
+};
+
+template <int BN, bool TA, bool TB, int STAGES>
+struct BgSmem {
+  static constexpr int kA = BM * BK * 4, kB = BN * BK * 4;
+  static constexpr int kARegion = kA * (TA ? 3 : 2);       // raw [, hi], lo
+  static constexpr int kBRegion = kB * (TB ? 3 : 2);
+  static constexpr int kStage = kARegion + kBRegion;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kTotal = STAGES * kStage + kBarBytes + 1024;
+};
+
+__device__ __forceinline__ float lo_part(float v) { return v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
+
+// raw: f32 tile in the swizzled K-major layout the MMA reads; lo gets the same layout.
+__device__ __forceinline__ void split_plain(const uint8_t* raw, uint8_t* lo, int bytes, int t) {
+  const float4* r = reinterpret_cast<const float4*>(raw);
+  float4* l = reinterpret_cast<float4*>(lo);
+#pragma unroll 4
+  for (int i = t; i < bytes / 16; i += 128) {
+    const float4 v = r[i];
+    l[i] = make_float4(lo_part(v.x), lo_part(v.y), lo_part(v.z), lo_part(v.w));
+  }
+}
+// raw: [32][W] f32, reduction index on rows. hi / lo: W rows of 128 bytes (K-major), 16-byte
+// chunk c of row n stored at chunk (c ^ (n & 7)) - the 128-byte swizzle. Lanes walk n, so the
+// reads are conflict-free and each quarter-warp's 128-bit stores cover all 32 banks.
+template <int W>
+__device__ __forceinline__ void split_transposed(const uint8_t* raw, uint8_t* hi, uint8_t* lo, int t) {
+  const float* r = reinterpret_cast<const float*>(raw);
+#pragma unroll 2
+  for (int i = t; i < W * 8; i += 128) {
+    const int n = i % W, k4 = i / W;
+    const float v0 = r[(4 * k4 + 0) * W + n], v1 = r[(4 * k4 + 1) * W + n];
+    const float v2 = r[(4 * k4 + 2) * W + n], v3 = r[(4 * k4 + 3) * W + n];
+    const int off = n * 128 + ((k4 ^ (n & 7)) << 4);
+    *reinterpret_cast<float4*>(hi + off) = make_float4(v0, v1, v2, v3);
+    *reinterpret_cast<float4*>(lo + off) = make_float4(lo_part(v0), lo_part(v1), lo_part(v2), lo_part(v3));
+  }
+}
+
+template <int BN, bool TA, bool TB, int STAGES>
+__global__ void __launch_bounds__(kThreadsTC)
+bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                const __grid_constant__ CUtensorMap mapC, BgParams p) {
+  using S = BgSmem<BN, TA, TB, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + STAGES * S::kStage;
+  auto bar_full = [&](int s) { return bars + 8u * s; };
+  auto bar_split = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+  const uint32_t bar_accum = bars + 8u * (3 * STAGES);
+  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 1);
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (3 * STAGES + 1));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int bi = blockIdx.z / p.H, hd = blockIdx.z % p.H;
+  int kb_begin = 0, kb_end = p.nkb;
+  if (p.causal == 1 && n0 > m0 + BM - 1) kb_end = 0;
+  if (p.causal == 2) kb_end = min(kb_end, (m0 + BM) / BK);
+  if (p.causal == 3) kb_begin = min(kb_end, m0 / BK);
+  const int nk = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_split(s), 128);
+      mbar_init(bar_empty(s), 1);
+    }
+    mbar_init(bar_accum, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  auto a_raw = [&](int s) { return (uint32_t)(s * S::kStage); };
+  auto a_hi = [&](int s) { return (uint32_t)(s * S::kStage + (TA ? S::kA : 0)); };
+  auto a_lo = [&](int s) { return (uint32_t)(s * S::kStage + (TA ? 2 : 1) * S::kA); };
+  auto b_raw = [&](int s) { return (uint32_t)(s * S::kStage + S::kARegion); };
+  auto b_hi = [&](int s) { return (uint32_t)(s * S::kStage + S::kARegion + (TB ? S::kB : 0)); };
+  auto b_lo = [&](int s) { return (uint32_t)(s * S::kStage + S::kARegion + (TB ? 2 : 1) * S::kB); };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int ax0 = bi * p.ax[0] + hd * p.ax[1], ay0 = bi * p.ay[0] + hd * p.ay[1];
+      const int bx0 = bi * p.bx[0] + hd * p.bx[1], by0 = bi * p.by[0] + hd * p.by[1];
+      int issued = 0;
+      bool ok = true;
+      for (int i = 0; i < nk && ok; ++i) {
+        const int s = i % STAGES, r = i / STAGES, k0 = (kb_begin + i) * BK;
+        if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 11);
+        if (!ok) break;
+        mbar_expect_tx(bar_full(s), S::kA + S::kB);
+        if (TA) tma_load_2d(base + a_raw(s), &mapA, bar_full(s), ax0 + m0, ay0 + k0);
+        else tma_load_2d(base + a_raw(s), &mapA, bar_full(s), ax0 + k0, ay0 + m0);
+        if (TB) tma_load_2d(base + b_raw(s), &mapB, bar_full(s), bx0 + n0, by0 + k0);
+        else tma_load_2d(base + b_raw(s), &mapB, bar_full(s), bx0 + k0, by0 + n0);
+        ++issued;
+      }
+      if (!ok) {
+        for (int i = (issued > STAGES ? issued - STAGES : 0); i < issued; ++i)
+          mbar_wait(bar_full(i % STAGES), (i / STAGES) & 1, p.err, 15);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_tf32(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < nk; ++i) {
+        const int s = i % STAGES, r = i / STAGES;
+        ok = mbar_wait(bar_split(s), r & 1, p.err, 12);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BK / 8; ++kk) {
+          const uint64_t da = smem_desc_sw128(base + a_hi(s) + kk * 32), db = smem_desc_sw128(base + b_hi(s) + kk * 32);
+          mma_tf32(tmem_base, da, db, idesc, (i | kk) != 0);
+          if (p.x3) {
+            mma_tf32(tmem_base, smem_desc_sw128(base + a_lo(s) + kk * 32), db, idesc, 1);
+            mma_tf32(tmem_base, da, smem_desc_sw128(base + b_lo(s) + kk * 32), idesc, 1);
+          }
+        }
+        mma_commit(bar_empty(s));
+      }
+      if (ok && nk > 0) mma_commit(bar_accum);
+    }
+  } else {
+    const int t = threadIdx.x - 64;
+    bool ok = true;
+    for (int i = 0; i < nk && ok; ++i) {
+      const int s = i % STAGES, r = i / STAGES;
+      ok = mbar_wait(bar_full(s), r & 1, p.err, 13);
+      if (!ok) break;
+      if (TA) split_transposed<BM>(base_ptr + a_raw(s), base_ptr + a_hi(s), base_ptr + a_lo(s), t);
+      else split_plain(base_ptr + a_raw(s), base_ptr + a_lo(s), S::kA, t);
+      if (TB) split_transposed<BN>(base_ptr + b_raw(s), base_ptr + b_hi(s), base_ptr + b_lo(s), t);
+      else split_plain(base_ptr + b_raw(s), base_ptr + b_lo(s), S::kB, t);
+      fence_async_smem();
+      mbar_arrive(bar_split(s));
+    }
+    if (ok && nk > 0) ok = mbar_wait(bar_accum, 0, p.err, 14);
+    tc_fence_after();
+    if (ok) {
+      // every product has retired, so the first stage's buffers serve as store staging
+      const int q = warp & 3, row0 = q * 32;
+      const uint32_t stage = base + q * 4096;
+      uint8_t* stage_ptr = base_ptr + q * 4096;
+      const int cx0 = bi * p.cx[0] + hd * p.cx[1], cy0 = bi * p.cy[0] + hd * p.cy[1];
+      const int m = m0 + row0 + lane;
+      for (int c = 0; c < BN / 32; ++c) {
+        const int ncol = n0 + c * 32;
+        uint32_t r[32];
+        if (nk > 0) {
+          tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float v = p.alpha * __uint_as_float(r[j]);
+            if (p.causal == 1 && ncol + j > m) v = 0.0f;
+            r[j] = __float_as_uint(v);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
         if (c > 0) {
-          if (lane == 0) tma_store_wait_read();   // the staging box of the previous chunk is free
+          if (lane == 0) tma_store_wait_read();
           __syncwarp();
         }
-        // row = lane; 16-byte chunk j lands at (j ^ (row & 7)): the 128-byte swizzle the store expects
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           uint4 v = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
@@ -333,7 +504,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(&mapC, stage, ncol, m0 + row0);
+          tma_store_2d(&mapC, stage, cx0 + ncol, cy0 + m0 + row0);
           tma_store_commit();
         }
       }
@@ -377,9 +548,10 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-// 2-D f32 row-major tensor [rows, cols] (cols contiguous), box [box_rows, box_cols], 128-byte swizzle.
+// 2-D f32 row-major tensor [rows, cols] (cols contiguous), box [box_rows, box_cols], 128-byte swizzle
+// (box_cols = 32) or none.
 bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
-              uint32_t box_cols) {
+              uint32_t box_cols, bool swizzle = true) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {cols, rows};
@@ -387,7 +559,8 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, u
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t elem[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -395,19 +568,21 @@ struct TcState {
   int* err_dev = nullptr;
   bool attrs_set = false;
   bool usable = true;
-  std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t>, CUtensorMap> maps;
+  std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> maps;
 };
 std::map<seeml_b200_ctx*, TcState>& states() {
   static std::map<seeml_b200_ctx*, TcState> s;
   return s;
 }
 
-const CUtensorMap* cached_map(TcState& st, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  const auto key = std::make_tuple(ptr, rows, cols, box_rows);
+// box_cols == 32: swizzled K-major tile; any other width: an unswizzled tile (transposed operands).
+const CUtensorMap* cached_map(TcState& st, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                              uint32_t box_cols = 32) {
+  const auto key = std::make_tuple(ptr, rows, cols, box_rows, box_cols);
   auto it = st.maps.find(key);
   if (it != st.maps.end()) return &it->second;
   CUtensorMap m;
-  if (!make_map(&m, ptr, rows, cols, box_rows, 32)) return nullptr;
+  if (!make_map(&m, ptr, rows, cols, box_rows, box_cols, box_cols == 32)) return nullptr;
   return &st.maps.emplace(key, m).first->second;
 }
 
@@ -444,7 +619,7 @@ int launch_tc(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   if (!ma || !mb || !mc || !ma2 || !mb2) return -1;
   TcParams p{(int)g.M, (int)g.N, (int)g.K, (int)g.K2, g.bias, g.addend, g.act, st.err_dev};
   dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((g.M + BM - 1) / BM));
-  kern<<<grid, kThreadsTC, S::kTotal, c->stream>>>(*ma, *mb, *mc, *ma2, *mb2, p);
+  kern<<<grid, kThreadsV2, S::kTotal, c->stream>>>(*ma, *mb, *mc, *ma2, *mb2, p);
   return 1;
 }
 
@@ -480,6 +655,60 @@ int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g) {
   if (g.N >= 192) r = split ? launch_tc<256, true, 2>(c, *st, g) : launch_tc<256, false, 4>(c, *st, g);
   else r = split ? launch_tc<128, true, 3>(c, *st, g) : launch_tc<128, false, 6>(c, *st, g);
   if (r < 0) {   // tensor maps / attributes unavailable: leave the CUDA-core path in charge
+    st->usable = false;
+    return 0;
+  }
+  return 1;
+}
+
+namespace {
+template <int BN, bool TA, bool TB, int STAGES>
+int launch_bg(seeml_b200_ctx* c, TcState& st, const TcBatched& g) {
+  using S = BgSmem<BN, TA, TB, STAGES>;
+  auto kern = bgemm_tc_kernel<BN, TA, TB, STAGES>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+    attr_done = true;
+  }
+  const CUtensorMap* ma = TA ? cached_map(st, g.A, g.a_rows, g.a_cols, BK, BM) : cached_map(st, g.A, g.a_rows, g.a_cols, BM);
+  const CUtensorMap* mb = TB ? cached_map(st, g.B, g.b_rows, g.b_cols, BK, BN) : cached_map(st, g.B, g.b_rows, g.b_cols, BN);
+  const CUtensorMap* mc = cached_map(st, g.C, g.c_rows, g.c_cols, 32);
+  if (!ma || !mb || !mc) return -1;
+  BgParams p{};
+  p.nkb = g.K / BK; p.causal = g.causal; p.alpha = g.alpha; p.H = g.H;
+  for (int i = 0; i < 2; ++i) {
+    p.ax[i] = g.ax[i]; p.ay[i] = g.ay[i]; p.bx[i] = g.bx[i]; p.by[i] = g.by[i]; p.cx[i] = g.cx[i]; p.cy[i] = g.cy[i];
+  }
+  p.x3 = c->gemm_kind == SEEML_B200_GEMM_TF32X3;
+  p.err = st.err_dev;
+  dim3 grid((unsigned)(g.N / BN), (unsigned)(g.M / BM), (unsigned)g.batch);
+  kern<<<grid, kThreadsTC, S::kTotal, c->stream>>>(*ma, *mb, *mc, p);
+  return 1;
+}
+}  // namespace
+
+// Batched per-head product on the tensor cores. 1 = launched, 0 = shape / context not
+// eligible (the caller's CUDA-core path runs instead).
+int gemm_tc_batched(seeml_b200_ctx* c, const TcBatched& g) {
+  if (c->gemm_kind != SEEML_B200_GEMM_TF32X3 && c->gemm_kind != SEEML_B200_GEMM_TF32) return 0;
+  if (g.M % BM != 0 || g.N % 64 != 0 || g.K % BK != 0 || g.M <= 0 || g.N <= 0 || g.K <= 0) return 0;
+  if (g.batch <= 0 || g.batch > 65535 || g.H <= 0) return 0;
+  if ((g.a_cols | g.b_cols | g.c_cols) % 4 != 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B) | reinterpret_cast<uintptr_t>(g.C)) & 15)
+    return 0;
+  if ((g.a_rows | g.a_cols | g.b_rows | g.b_cols | g.c_rows | g.c_cols) >> 31) return 0;   // 32-bit TMA coordinates
+  if (g.a_t && !g.b_t) return 0;
+  TcState* st = state_of(c, false);
+  if (!st || !st->usable || !st->err_dev) return 0;
+  int r;
+  if (g.a_t) r = launch_bg<64, true, true, 3>(c, *st, g);
+  else if (g.b_t) r = launch_bg<64, false, true, 4>(c, *st, g);
+  else r = launch_bg<64, false, false, 2>(c, *st, g);
+  if (r < 0) {
     st->usable = false;
     return 0;
   }

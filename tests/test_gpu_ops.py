@@ -58,11 +58,28 @@ def test_gemm_family_matches_oracle(gemm):
         _compare(c, want, got)
 
 
-def test_attention_family_large_shapes():
+@pytest.mark.parametrize("gemm", [0, 2], ids=["tf32x3", "fp32_simt"])
+def test_attention_family_large_shapes(gemm):
+    """Sequence lengths that are multiples of 128 with 64-wide heads take the batched
+    tensor-core kernel (3xTF32, transposed operands re-laid in shared memory); the CUDA-core
+    kernel is held to the tight per-case tolerance, the tensor-core one to the stated one."""
     rng = np.random.default_rng(5)
     for c in opcases.attention_cases(rng, big=True)[-14:]:
-        want, got = _run_case(c, gemm=0)
+        want, got = _run_case(c, gemm=gemm)
+        if gemm == 0 and c.name.startswith("ATTN_"):
+            c.rtol, c.atol = max(c.rtol, 1e-3), max(c.atol, 1e-4)
         _compare(c, want, got)
+
+
+def test_masked_entries_stay_exact_zeros_on_the_tensor_core_path():
+    rng = np.random.default_rng(9)
+    cases = opcases.attention_cases(rng, big=True)
+    for prefix, key in (("ATTN_FWD_1x512", "P"), ("ATTN_DP_1x512", "dP")):
+        c = next(c for c in cases if c.name.startswith(prefix))
+        _, got = _run_case(c, gemm=0)
+        P = opcases.read_output(got, c.outputs[key]).reshape(-1, 512, 512)
+        iu = np.triu_indices(512, 1)
+        assert np.all(P[:, iu[0], iu[1]] == 0.0), prefix
 
 
 def test_masked_attention_entries_are_exact_zeros():
