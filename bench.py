@@ -38,6 +38,10 @@ CONFIGS = {
                rank=16, alpha=32.0, targets=("wq", "wk", "wv", "wo"), lr=5e-4),
     "c4": dict(kind="llama", vocab=32000, d=1024, heads=16, ffn=2816, layers=12, seq=512, seqs=32,
                chunks=8, rank=16, alpha=32.0, targets=("wq", "wk", "wv", "wo", "w_up", "w_down"), lr=3e-4),
+    # two layers of c4 with a smaller vocabulary: the same per-layer kernel shapes in a few GB, sized for
+    # profiler captures (not a bench line)
+    "c4-slice": dict(kind="llama", vocab=8192, d=1024, heads=16, ffn=2816, layers=2, seq=512, seqs=32,
+                     chunks=1, rank=16, alpha=32.0, targets=("wq", "wk", "wv", "wo", "w_up", "w_down"), lr=3e-4),
 }
 
 

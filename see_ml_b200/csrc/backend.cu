@@ -136,6 +136,33 @@ inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) 
 
 // Rank-r shapes go to the dedicated kernels. Returns the launch count, or 0 when the
 // instruction is not one of those shapes.
+// Rank-r products: the tensor-core kernels when the shape allows, else the CUDA-core ones.
+// Both return the number of kernels launched.
+int rank_n(seeml_b200_ctx* c, const float* A, const float* B, float* out, int M, int n, int K, int b_is_nk,
+           float alpha) {
+  const float* bnk = B;
+  int extra = 0;
+  if (!b_is_nk && n >= 16 && M >= 1024) {
+    float* t = gemm_tc_rank_scratch(c, (uint64_t)n * K);
+    if (t) {
+      gemm_tc_transpose(c, B, t, K, n);
+      bnk = t;
+      extra = 1;
+    } else {
+      bnk = nullptr;
+    }
+  }
+  if (bnk && gemm_tc_rank_n(c, A, bnk, out, M, n, K, alpha) == 1) return 1 + extra;
+  return extra + k::skinny_n(A, B, out, M, n, K, b_is_nk, alpha, c->stream);
+}
+int rank_tn(seeml_b200_ctx* c, const float* W, const float* S, float* out, int T, int big, int small,
+            int transposed, float alpha) {
+  const uint64_t rows = gemm_tc_rank_tn_chunk_rows(T, big, small);
+  if (rows && gemm_tc_rank_tn(c, W, S, c->gemm_ws, T, big, small, rows) == 1)
+    return 1 + k::skinny_tn_reduce_bs(c->gemm_ws, out, (int)(T / rows), big, small, transposed, alpha, c->stream);
+  return k::skinny_tn(W, S, out, c->gemm_ws, T, big, small, transposed, alpha, c->stream);
+}
+
 int try_skinny(const Exec& x, const Instr& ins, bool launch, uint64_t* ws_need) {
   if (ins.opcode != kGemmNN && ins.opcode != kGemmNT && ins.opcode != kGemmTN) return 0;
   if (ins.flags != 0) return 0;
@@ -151,16 +178,16 @@ int try_skinny(const Exec& x, const Instr& ins, bool launch, uint64_t* ws_need) 
     // C[M,N] = A[K,M]^T B[K,N]; the reduction runs over the K rows
     if (N <= M && k::skinny_tn_ok(K, M, N)) {
       if (ws_need) *ws_need = k::skinny_tn_workspace_floats(K, M, N);
-      return launch ? k::skinny_tn(A, B, C, x.c->gemm_ws, K, M, N, 1, 1.0f, st) : 2;
+      return launch ? rank_tn(x.c, A, B, C, K, M, N, 1, 1.0f) : 2;
     }
     if (M < N && k::skinny_tn_ok(K, N, M)) {
       if (ws_need) *ws_need = k::skinny_tn_workspace_floats(K, N, M);
-      return launch ? k::skinny_tn(B, A, C, x.c->gemm_ws, K, N, M, 0, 1.0f, st) : 2;
+      return launch ? rank_tn(x.c, B, A, C, K, N, M, 0, 1.0f) : 2;
     }
     return 0;
   }
   const int b_is_nk = ins.opcode == kGemmNT;
-  if (k::skinny_n_ok(M, N, K) && al16(A)) return launch ? k::skinny_n(A, B, C, M, N, K, b_is_nk, 1.0f, st) : 1;
+  if (k::skinny_n_ok(M, N, K) && al16(A)) return launch ? rank_n(x.c, A, B, C, M, N, K, b_is_nk, 1.0f) : 1;
   if (k::skinny_k_ok(M, N, K) && al16(C)) return launch ? k::skinny_k(A, B, nullptr, C, M, N, K, b_is_nk, 1.0f, st) : 1;
   return 0;
 }

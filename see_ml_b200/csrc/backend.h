@@ -46,6 +46,7 @@ struct TcGemm {
   uint64_t M, N, K;
   const float* A2; const float* B2t; uint64_t K2;
   const float* addend; const float* bias; int act;
+  float alpha;                                  // 0 is read as 1 (zero-initialised descriptors)
 };
 bool gemm_tc_shape_ok(const seeml_b200_ctx* c, uint64_t M, uint64_t N, uint64_t K);
 // Batched per-head product C_z = alpha * A_z . B_z (z = b * H + h); every operand is a window
@@ -61,6 +62,16 @@ struct TcBatched {
   float alpha;
 };
 int gemm_tc_batched(seeml_b200_ctx* c, const TcBatched& g);
+// Rank-r (LoRA factor) products on the tensor cores; each returns 1 when launched, 0 when the
+// shape is not eligible. rank_n: out[M,n] = alpha A[M,K] Bnk[n,K]^T. rank_tn: per-chunk partial
+// sums partial[chunk][big][small] of W[T,big]^T S[T,small] over chunk_rows rows each.
+int gemm_tc_rank_n(seeml_b200_ctx* c, const float* A, const float* Bnk, float* out, uint64_t M, uint64_t n,
+                   uint64_t K, float alpha);
+float* gemm_tc_rank_scratch(seeml_b200_ctx* c, uint64_t floats);
+void gemm_tc_transpose(seeml_b200_ctx* c, const float* in, float* out, uint64_t K, uint64_t N);
+uint64_t gemm_tc_rank_tn_chunk_rows(uint64_t T, uint64_t big, uint64_t small);
+int gemm_tc_rank_tn(seeml_b200_ctx* c, const float* W, const float* S, float* partial, uint64_t T, uint64_t big,
+                    uint64_t small, uint64_t chunk_rows);
 int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g);
 const float* gemm_tc_transposed_weight(seeml_b200_ctx* c, uint64_t rodata_off, uint64_t K, uint64_t N, bool create);
 

@@ -43,6 +43,7 @@ struct TcParams {
   const float* bias;     // nullable, length N
   const float* addend;   // nullable, [M,N] row-major: C = addend + A.B^T (+ A2.B2^T)
   int act;               // 0 none 1 relu 2 gelu 3 silu
+  float alpha;           // scales the product before addend / bias / activation
   int* err;              // device error word
 };
 
@@ -72,7 +73,7 @@ struct Smem {
   static constexpr int kBBytes = BN * BK * 4;
   static constexpr int kRawBytes = kABytes + kBBytes;
   static constexpr int kStageBytes = kRawBytes * (SPLIT ? 2 : 1);
-  static constexpr int kEpiBytes = 8 * 32 * 128;          // one 32x32 f32 box per worker warp (aliases stage 0)
+  static constexpr int kEpiBytes = BM * (BN < 32 ? 32 : BN) * 4;   // store staging, aliases the stage buffers
   static constexpr int kBarBytes = 256;
   static constexpr int kTotal = STAGES * kStageBytes + kBarBytes + 1024;  // + alignment slack
   static_assert(STAGES * kStageBytes >= kEpiBytes, "store staging must fit in the stage buffers");
@@ -117,8 +118,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -189,7 +191,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     const int q = warp & 3;                     // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;           // which half of the tile's columns it owns
     const int row0 = q * 32;
-    constexpr int NH = BN / 2;
+    constexpr int NH = BN >= 64 ? BN / 2 : BN;  // columns per collecting warp (narrow tiles: warps 2..5 only)
+    constexpr int LD = NH >= 32 ? 32 : 16;      // columns per TMEM load / store box
+    const bool collector = half * NH < BN;
     float acc[NH];
 #pragma unroll
     for (int j = 0; j < NH; ++j) acc[j] = 0.0f;
@@ -199,13 +203,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       const int buf = ci & 1;
       if (!mbar_wait(bar_acc_full(buf), (ci >> 1) & 1, p.err, 4)) return false;
       tc_fence_after();
+      if (collector) {
 #pragma unroll
-      for (int c = 0; c < NH / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + buf * BN + half * NH + c * 32, r);
-        tmem_ld_wait();
+        for (int c = 0; c < NH / LD; ++c) {
+          uint32_t r[32];
+          tmem_ld_cols<LD>(tmem_base + ((uint32_t)row0 << 16) + buf * BN + half * NH + c * LD, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[c * 32 + j] += __uint_as_float(r[j]);
+          for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]);
+        }
       }
       tc_fence_before();
       mbar_arrive(bar_acc_empty(buf));
@@ -240,21 +246,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       }
     }
     for (; ok && collected < nchunks; ++collected) ok = collect(collected);
-    if (ok && m0 + row0 < p.M) {
-      // every product has retired (the last chunk was collected): stage 0 serves as store staging
-      const uint32_t stage = base + (warp - 2) * 4096;
-      uint8_t* stage_ptr = base_ptr + (warp - 2) * 4096;
+    if (ok && collector && m0 + row0 < p.M) {
+      // every product has retired (the last chunk was collected), so the stage buffers serve as
+      // store staging: one 32x32 box per (warp, column chunk), all stores in flight together
 #pragma unroll
-      for (int c = 0; c < NH / 32; ++c) {
-        const int ncol = n0 + half * NH + c * 32;
+      for (int c = 0; c < NH / LD; ++c) {
+        const int ncol = n0 + half * NH + c * LD;
         if (ncol < p.N) {
+          const uint32_t box = (uint32_t)(((warp - 2) * (NH / LD) + c) * 4096);
+          uint8_t* stage_ptr = base_ptr + box;
           uint32_t r[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(acc[c * 32 + j]);
+          for (int j = 0; j < LD; ++j) r[j] = __float_as_uint(p.alpha * acc[c * LD + j]);
           if (p.addend != nullptr && m0 + row0 + lane < p.M) {
             const float* arow = p.addend + (size_t)(m0 + row0 + lane) * p.N + ncol;
 #pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4) {
+            for (int j4 = 0; j4 < LD / 4; ++j4) {
               if (ncol + 4 * j4 < p.N) {          // N is a multiple of 4
                 const float4 d = *reinterpret_cast<const float4*>(arow + 4 * j4);
                 r[4 * j4 + 0] = __float_as_uint(d.x + __uint_as_float(r[4 * j4 + 0]));
@@ -266,26 +273,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           }
           if (p.bias != nullptr || p.act != 0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
+            for (int j = 0; j < LD; ++j) {
               float v = __uint_as_float(r[j]);
               if (p.bias != nullptr && ncol + j < p.N) v = v + p.bias[ncol + j];
               r[j] = __float_as_uint(epi_act(p.act, v));
             }
           }
-          if (c > 0) {
-            if (lane == 0) tma_store_wait_read();   // the staging box of the previous chunk is free
-            __syncwarp();
-          }
           // row = lane; 16-byte chunk j lands at (j ^ (row & 7)): the 128-byte swizzle the store expects
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < LD / 4; ++j) {
             uint4 v = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
             *reinterpret_cast<uint4*>(stage_ptr + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
           }
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&mapC, stage, ncol, m0 + row0);
+            tma_store_2d(&mapC, base + box, ncol, m0 + row0);
             tma_store_commit();
           }
         }
@@ -295,7 +298,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 // ------------------------------------------------- batched per-head products (attention)
@@ -370,10 +373,11 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   auto bar_full = [&](int s) { return bars + 8u * s; };
   auto bar_split = [&](int s) { return bars + 8u * (STAGES + s); };
   auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
-  const uint32_t bar_accum = bars + 8u * (3 * STAGES);
-  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 1);
+  auto bar_acc_full = [&](int b) { return bars + 8u * (3 * STAGES + b); };
+  auto bar_acc_empty = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 4);
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (3 * STAGES + 1));
+      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (3 * STAGES + 4));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
@@ -390,11 +394,16 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       mbar_init(bar_split(s), 128);
       mbar_init(bar_empty(s), 1);
     }
-    mbar_init(bar_accum, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), 128);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators, chunks alternate
+  constexpr int LD = BN >= 32 ? 32 : 16;       // columns per TMEM load / store box
   if (warp == 1) {
-    tmem_alloc(tmem_slot, BN);
+    tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -437,25 +446,56 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       bool ok = true;
       for (int i = 0; i < nk; ++i) {
         const int s = i % STAGES, r = i / STAGES;
+        const int ci = i / kChunk, buf = ci & 1;
+        if (i % kChunk == 0 && ci >= 2) {
+          ok = mbar_wait(bar_acc_empty(buf), ((ci >> 1) - 1) & 1, p.err, 16);
+          if (!ok) break;
+          tc_fence_after();
+        }
         ok = mbar_wait(bar_split(s), r & 1, p.err, 12);
         if (!ok) break;
         tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
 #pragma unroll
         for (int kk = 0; kk < BK / 8; ++kk) {
           const uint64_t da = smem_desc_sw128(base + a_hi(s) + kk * 32), db = smem_desc_sw128(base + b_hi(s) + kk * 32);
-          mma_tf32(tmem_base, da, db, idesc, (i | kk) != 0);
+          mma_tf32(tmem_d, da, db, idesc, ((i % kChunk) | kk) != 0);
           if (p.x3) {
-            mma_tf32(tmem_base, smem_desc_sw128(base + a_lo(s) + kk * 32), db, idesc, 1);
-            mma_tf32(tmem_base, da, smem_desc_sw128(base + b_lo(s) + kk * 32), idesc, 1);
+            mma_tf32(tmem_d, smem_desc_sw128(base + a_lo(s) + kk * 32), db, idesc, 1);
+            mma_tf32(tmem_d, da, smem_desc_sw128(base + b_lo(s) + kk * 32), idesc, 1);
           }
         }
         mma_commit(bar_empty(s));
+        if (i % kChunk == kChunk - 1 || i == nk - 1) mma_commit(bar_acc_full(buf));
       }
-      if (ok && nk > 0) mma_commit(bar_accum);
     }
   } else {
     const int t = threadIdx.x - 64;
+    const int q = warp & 3, row0 = q * 32;
     bool ok = true;
+    // finished chunks are added into f32 registers while the next chunk is multiplied (the
+    // tensor core's own accumulation truncates; see gemm_tc_kernel)
+    float acc[BN];
+#pragma unroll
+    for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
+    const int nchunks = (nk + kChunk - 1) / kChunk;
+    int collected = 0;
+    auto collect = [&](int ci) {
+      const int buf = ci & 1;
+      if (!mbar_wait(bar_acc_full(buf), (ci >> 1) & 1, p.err, 14)) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < BN / LD; ++c) {
+        uint32_t r[32];
+        tmem_ld_cols<LD>(tmem_base + ((uint32_t)row0 << 16) + buf * BN + c * LD, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]);
+      }
+      tc_fence_before();
+      mbar_arrive(bar_acc_empty(buf));
+      return true;
+    };
     for (int i = 0; i < nk && ok; ++i) {
       const int s = i % STAGES, r = i / STAGES;
       ok = mbar_wait(bar_full(s), r & 1, p.err, 13);
@@ -466,38 +506,33 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       else split_plain(base_ptr + b_raw(s), base_ptr + b_lo(s), S::kB, t);
       fence_async_smem();
       mbar_arrive(bar_split(s));
+      if (i % kChunk == 1 && i > kChunk) {
+        ok = collect(collected);
+        ++collected;
+      }
     }
-    if (ok && nk > 0) ok = mbar_wait(bar_accum, 0, p.err, 14);
-    tc_fence_after();
+    for (; ok && collected < nchunks; ++collected) ok = collect(collected);
     if (ok) {
       // every product has retired, so the first stage's buffers serve as store staging
-      const int q = warp & 3, row0 = q * 32;
       const uint32_t stage = base + q * 4096;
       uint8_t* stage_ptr = base_ptr + q * 4096;
       const int cx0 = bi * p.cx[0] + hd * p.cx[1], cy0 = bi * p.cy[0] + hd * p.cy[1];
       const int m = m0 + row0 + lane;
-      for (int c = 0; c < BN / 32; ++c) {
-        const int ncol = n0 + c * 32;
+      for (int c = 0; c < BN / LD; ++c) {
+        const int ncol = n0 + c * LD;
         uint32_t r[32];
-        if (nk > 0) {
-          tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + c * 32, r);
-          tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float v = p.alpha * __uint_as_float(r[j]);
-            if (p.causal == 1 && ncol + j > m) v = 0.0f;
-            r[j] = __float_as_uint(v);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        for (int j = 0; j < LD; ++j) {
+          float v = p.alpha * acc[c * LD + j];          // empty reduction ranges leave exact zeros
+          if (p.causal == 1 && ncol + j > m) v = 0.0f;
+          r[j] = __float_as_uint(v);
         }
         if (c > 0) {
           if (lane == 0) tma_store_wait_read();
           __syncwarp();
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < LD / 4; ++j) {
           uint4 v = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
           *reinterpret_cast<uint4*>(stage_ptr + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
         }
@@ -513,7 +548,7 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, BN);
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 // [K,N] row-major -> [N,K] row-major (one-time copy of a frozen weight).
@@ -568,6 +603,7 @@ struct TcState {
   int* err_dev = nullptr;
   bool attrs_set = false;
   bool usable = true;
+  float* rank_scratch = nullptr;
   std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> maps;
 };
 std::map<seeml_b200_ctx*, TcState>& states() {
@@ -575,14 +611,15 @@ std::map<seeml_b200_ctx*, TcState>& states() {
   return s;
 }
 
-// box_cols == 32: swizzled K-major tile; any other width: an unswizzled tile (transposed operands).
+// Default: a swizzled K-major tile 32 elements wide; box_cols != 0 asks for an unswizzled tile of
+// that width (operands stored with the reduction index on rows).
 const CUtensorMap* cached_map(TcState& st, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                              uint32_t box_cols = 32) {
+                              uint32_t box_cols = 0) {
   const auto key = std::make_tuple(ptr, rows, cols, box_rows, box_cols);
   auto it = st.maps.find(key);
   if (it != st.maps.end()) return &it->second;
   CUtensorMap m;
-  if (!make_map(&m, ptr, rows, cols, box_rows, box_cols, box_cols == 32)) return nullptr;
+  if (!make_map(&m, ptr, rows, cols, box_rows, box_cols ? box_cols : 32, box_cols == 0)) return nullptr;
   return &st.maps.emplace(key, m).first->second;
 }
 
@@ -617,7 +654,7 @@ int launch_tc(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   const CUtensorMap* ma2 = g.K2 ? cached_map(st, g.A2, g.M, g.K2, BM) : ma;
   const CUtensorMap* mb2 = g.K2 ? cached_map(st, g.B2t, g.N, g.K2, BN) : mb;
   if (!ma || !mb || !mc || !ma2 || !mb2) return -1;
-  TcParams p{(int)g.M, (int)g.N, (int)g.K, (int)g.K2, g.bias, g.addend, g.act, st.err_dev};
+  TcParams p{(int)g.M, (int)g.N, (int)g.K, (int)g.K2, g.bias, g.addend, g.act, g.alpha == 0.0f ? 1.0f : g.alpha, st.err_dev};
   dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((g.M + BM - 1) / BM));
   kern<<<grid, kThreadsV2, S::kTotal, c->stream>>>(*ma, *mb, *mc, *ma2, *mb2, p);
   return 1;
@@ -715,6 +752,92 @@ int gemm_tc_batched(seeml_b200_ctx* c, const TcBatched& g) {
   return 1;
 }
 
+// ---- rank-r (LoRA factor) products on the tensor cores -------------------------------------
+// out[M,n] = alpha * A[M,K] . Bnk[n,K]^T for n in {16, 32, 64}: one CTA per 128 rows streams
+// A once through a deep TMA ring (HBM-bound). 1 = launched, 0 = not eligible.
+int gemm_tc_rank_n(seeml_b200_ctx* c, const float* A, const float* Bnk, float* out, uint64_t M, uint64_t n,
+                   uint64_t K, float alpha) {
+  if (c->gemm_kind != SEEML_B200_GEMM_TF32X3 && c->gemm_kind != SEEML_B200_GEMM_TF32) return 0;
+  if ((n != 16 && n != 32 && n != 64) || M < 1024 || K < 128 || K % 4 != 0) return 0;
+  if (M > 0x7FFFFFFF || K > 0x7FFFFFFF) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bnk) | reinterpret_cast<uintptr_t>(out)) & 15) return 0;
+  TcState* st = state_of(c, false);
+  if (!st || !st->usable || !st->err_dev) return 0;
+  TcGemm g{};
+  g.A = A; g.Bt = Bnk; g.C = out; g.M = M; g.N = n; g.K = K; g.alpha = alpha;
+  const bool split = c->gemm_kind == SEEML_B200_GEMM_TF32X3;
+  int r;
+  if (n == 16) r = split ? launch_tc<16, true, 6>(c, *st, g) : launch_tc<16, false, 8>(c, *st, g);
+  else if (n == 32) r = split ? launch_tc<32, true, 5>(c, *st, g) : launch_tc<32, false, 8>(c, *st, g);
+  else r = split ? launch_tc<64, true, 4>(c, *st, g) : launch_tc<64, false, 8>(c, *st, g);
+  if (r < 0) {
+    st->usable = false;
+    return 0;
+  }
+  return 1;
+}
+
+// Scratch for the [n,K] copy of a rank-r factor stored [K,n] (at most kRankScratchFloats).
+constexpr uint64_t kRankScratchFloats = 64 * 8192;
+float* gemm_tc_rank_scratch(seeml_b200_ctx* c, uint64_t floats) {
+  TcState* st = state_of(c, false);
+  if (!st || floats > kRankScratchFloats) return nullptr;
+  if (!st->rank_scratch && cudaMalloc(&st->rank_scratch, kRankScratchFloats * sizeof(float)) != cudaSuccess) {
+    cudaGetLastError();
+    st->rank_scratch = nullptr;
+  }
+  return st->rank_scratch;
+}
+void gemm_tc_transpose(seeml_b200_ctx* c, const float* in, float* out, uint64_t K, uint64_t N) {
+  dim3 grid((unsigned)((N + 31) / 32), (unsigned)((K + 31) / 32)), block(32, 8);
+  transpose_kernel<<<grid, block, 0, c->stream>>>(in, out, (int)K, (int)N);
+}
+
+// Rows per reduction chunk of the rank-r TN product: a function of the shape only (fills
+// whole waves of 148 CTAs as far as the divisors of T allow), 0 when not eligible.
+uint64_t gemm_tc_rank_tn_chunk_rows(uint64_t T, uint64_t big, uint64_t small) {
+  if ((small != 16 && small != 32 && small != 64) || big % BM != 0 || big < BM || T < 4096) return 0;
+  uint64_t best = 0;
+  double best_eff = 0.0;
+  for (uint64_t rows : {2048ull, 1024ull, 512ull}) {
+    if (T % rows != 0) continue;
+    const uint64_t ctas = (T / rows) * (big / BM), waves = (ctas + 147) / 148;
+    const double eff = (double)ctas / (double)(waves * 148);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = rows; }
+  }
+  return best;
+}
+
+// partial[chunk][big][small] = sum over the chunk's rows t of W[t,big]^T S[t,small]; both
+// operands are stored with the reduction index on rows and are re-laid K-major in shared
+// memory. The caller sums the chunks in order. 1 = launched, 0 = not eligible.
+int gemm_tc_rank_tn(seeml_b200_ctx* c, const float* W, const float* S, float* partial, uint64_t T, uint64_t big,
+                    uint64_t small, uint64_t chunk_rows) {
+  if (c->gemm_kind != SEEML_B200_GEMM_TF32X3 && c->gemm_kind != SEEML_B200_GEMM_TF32) return 0;
+  if (chunk_rows == 0 || T % chunk_rows != 0 || chunk_rows % BK != 0) return 0;
+  const uint64_t chunks = T / chunk_rows;
+  if (chunks > 65535 || chunks * big > 0x7FFFFFFF || T > 0x7FFFFFFF) return 0;
+  if ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(S) | reinterpret_cast<uintptr_t>(partial)) & 15) return 0;
+  TcState* st = state_of(c, false);
+  if (!st || !st->usable || !st->err_dev) return 0;
+  TcBatched g{};
+  g.A = W; g.B = S; g.C = partial;
+  g.a_rows = T; g.a_cols = big; g.b_rows = T; g.b_cols = small; g.c_rows = chunks * big; g.c_cols = small;
+  g.a_t = true; g.b_t = true;
+  g.ay[0] = (int)chunk_rows; g.by[0] = (int)chunk_rows; g.cy[0] = (int)big;
+  g.M = (int)big; g.N = (int)small; g.K = (int)chunk_rows; g.batch = (int)chunks; g.H = 1; g.causal = 0;
+  g.alpha = 1.0f;
+  int r;
+  if (small == 16) r = launch_bg<16, true, true, 4>(c, *st, g);
+  else if (small == 32) r = launch_bg<32, true, true, 3>(c, *st, g);
+  else r = launch_bg<64, true, true, 3>(c, *st, g);
+  if (r < 0) {
+    st->usable = false;
+    return 0;
+  }
+  return 1;
+}
+
 // Transposed [N,K] copy of the frozen weight at `rodata_off` ([K,N]); made on first request.
 const float* gemm_tc_transposed_weight(seeml_b200_ctx* c, uint64_t rodata_off, uint64_t K, uint64_t N, bool create) {
   const auto key = std::make_tuple(rodata_off, K, N);
@@ -785,6 +908,7 @@ void gemm_tensor_core_release(seeml_b200_ctx* c) {
   auto sit = states().find(c);
   if (sit == states().end()) return;
   cudaFree(sit->second.err_dev);
+  cudaFree(sit->second.rank_scratch);
   states().erase(sit);
 }
 

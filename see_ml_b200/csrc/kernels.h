@@ -120,6 +120,8 @@ int skinny_k(const float* A, const float* B, const float* addend, float* out, in
 // R[s,b] = alpha * sum_t S[t,s] * W[t,b]; stored [small,big], or [big,small] when transposed
 int skinny_tn(const float* W, const float* S, float* out, float* workspace, int T, int big, int small,
               int transposed, float alpha, cudaStream_t st);
+int skinny_tn_reduce_bs(const float* workspace, float* out, int chunks, int big, int small, int transposed,
+                        float alpha, cudaStream_t st);
 
 }  // namespace k
 }  // namespace seeml_b200

@@ -215,15 +215,17 @@ __global__ void __launch_bounds__(256) skinny_tn_kernel(const float* __restrict_
   }
 }
 // out = alpha * (partials summed in chunk order); out is [small,big] or, transposed, [big,small].
+// The partials are [chunk][small][big], or [chunk][big][small] when ws_bs is set.
 __global__ void __launch_bounds__(256) skinny_tn_reduce_kernel(const float* __restrict__ partial,
                                                                float* __restrict__ out, int chunks, int big,
-                                                               int small, int transposed, float alpha) {
+                                                               int small, int transposed, float alpha, int ws_bs) {
   const int total = big * small;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    const int s = i / big, b = i % big;
+    // walk the index space in the partials' own order so the reads coalesce
+    const int s = ws_bs ? i % small : i / big, b = ws_bs ? i / small : i % big;
     float acc = 0.0f;
-    for (int ch = 0; ch < chunks; ++ch) acc += partial[((size_t)ch * small + s) * big + b];
-    out[transposed ? (size_t)b * small + s : (size_t)i] = alpha * acc;
+    for (int ch = 0; ch < chunks; ++ch) acc += partial[(size_t)ch * total + i];
+    out[transposed ? (size_t)b * small + s : (size_t)s * big + b] = alpha * acc;
   }
 }
 
@@ -264,8 +266,17 @@ int skinny_tn(const float* W, const float* S, float* out, float* workspace, int 
   else skinny_tn_kernel<32><<<grid, 256, 0, st>>>(W, S, workspace, T, big, small);
   int blocks = (big * small + 255) / 256;
   if (blocks > 1184) blocks = 1184;
-  skinny_tn_reduce_kernel<<<blocks, 256, 0, st>>>(workspace, out, chunks, big, small, transposed, alpha);
+  skinny_tn_reduce_kernel<<<blocks, 256, 0, st>>>(workspace, out, chunks, big, small, transposed, alpha, 0);
   return 2;
+}
+
+// Ordered sum of per-chunk partials laid out [chunk][big][small] (the tensor-core producer).
+int skinny_tn_reduce_bs(const float* workspace, float* out, int chunks, int big, int small, int transposed,
+                        float alpha, cudaStream_t st) {
+  int blocks = (big * small + 255) / 256;
+  if (blocks > 1184) blocks = 1184;
+  skinny_tn_reduce_kernel<<<blocks, 256, 0, st>>>(workspace, out, chunks, big, small, transposed, alpha, 1);
+  return 1;
 }
 
 }  // namespace k

@@ -150,6 +150,24 @@ def gemm_cases(rng, big=False):
         ins = _ins(op, [a, b, c, F.f32_bits(0.0123)], [M, N, K], flags=(2 << 1) if op == Op.GEMM_NN_Q8 else 0)
         ar, r = L.done()
         cases.append(Case(f"{op.name}", ins, ar, r, {"C": (c, M * N, np.float32)}))
+    if big:
+        # LoRA-factor shapes long enough for the tensor-core rank-r kernels (ragged M and K included)
+        for (M, N, K) in [(2048, 16, 1024), (1100, 32, 520), (1024, 64, 256)]:
+            for op in (Op.GEMM_NN, Op.GEMM_NT):
+                L = Layout()
+                a = L.put(_rn(rng, M, K))
+                b = L.put(_rn(rng, N, K) if op == Op.GEMM_NT else _rn(rng, K, N))
+                c = L.out(M * N)
+                ar, r = L.done()
+                cases.append(Case(f"{op.name}_rank_{M}x{N}x{K}", _ins(op, [a, b, c], [M, N, K]), ar, r,
+                                  {"C": (c, M * N, np.float32)}))
+        for (M, N, K) in [(16, 256, 4096), (384, 32, 8192), (128, 64, 4096)]:
+            L = Layout()
+            a, b = L.put(_rn(rng, K, M)), L.put(_rn(rng, K, N))
+            c = L.out(M * N)
+            ar, r = L.done()
+            cases.append(Case(f"GEMM_TN_rank_{M}x{N}x{K}", _ins(Op.GEMM_TN, [a, b, c], [M, N, K]), ar, r,
+                              {"C": (c, M * N, np.float32)}, rtol=1e-3, atol=5e-4))
     return cases
 
 
