@@ -23,6 +23,7 @@
 // backward GEMMs through frozen weights both take this K-major form.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "backend.h"
@@ -67,10 +68,10 @@ constexpr int kChunk = 4;              // k-blocks (x 32 elements) per TMEM accu
 constexpr int kWorkers = 256;          // threads of the 8 split / accumulate / epilogue warps
 constexpr int kThreadsV2 = 64 + kWorkers;
 
-template <int BN, bool SPLIT, int STAGES>
+template <int BN, bool SPLIT, int STAGES, int KB>
 struct Smem {
-  static constexpr int kABytes = BM * BK * 4;             // 16 KiB
-  static constexpr int kBBytes = BN * BK * 4;
+  static constexpr int kABytes = BM * KB * 4;             // 16 KiB at KB = 32
+  static constexpr int kBBytes = BN * KB * 4;
   static constexpr int kRawBytes = kABytes + kBBytes;
   static constexpr int kStageBytes = kRawBytes * (SPLIT ? 2 : 1);
   static constexpr int kEpiBytes = BM * (BN < 32 ? 32 : BN) * 4;   // store staging, aliases the stage buffers
@@ -79,12 +80,13 @@ struct Smem {
   static_assert(STAGES * kStageBytes >= kEpiBytes, "store staging must fit in the stage buffers");
 };
 
-template <int BN, bool SPLIT, int STAGES>
+template <int BN, bool SPLIT, int STAGES, int KB>
 __global__ void __launch_bounds__(kThreadsV2, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapA2,
                const __grid_constant__ CUtensorMap mapB2, TcParams p) {
-  using S = Smem<BN, SPLIT, STAGES>;
+  using S = Smem<BN, SPLIT, STAGES, KB>;
+  constexpr int kChunkBlocks = kChunk * (BK / KB);   // k-blocks per accumulation chunk (128 elements of K)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -102,9 +104,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   // k-blocks of the main pair, then of the low-rank pair (C += A2[M,K2] . B2[N,K2]^T): the
   // LoRA term rides the same accumulators as extra reduction steps
-  const int nkb1 = (p.K + BK - 1) / BK;
-  const int nkb = nkb1 + (p.K2 + BK - 1) / BK;
-  const int nchunks = (nkb + kChunk - 1) / kChunk;
+  const int nkb1 = (p.K + KB - 1) / KB;
+  const int nkb = nkb1 + (p.K2 + KB - 1) / KB;
+  const int nchunks = (nkb + kChunkBlocks - 1) / kChunkBlocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -140,11 +142,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const uint32_t a_dst = base + s * S::kStageBytes, b_dst = a_dst + S::kABytes;
         mbar_expect_tx(bar_full(s), S::kRawBytes);
         if (kb < nkb1) {
-          tma_load_2d(a_dst, &mapA, bar_full(s), kb * BK, m0);
-          tma_load_2d(b_dst, &mapB, bar_full(s), kb * BK, n0);
+          tma_load_2d(a_dst, &mapA, bar_full(s), kb * KB, m0);
+          tma_load_2d(b_dst, &mapB, bar_full(s), kb * KB, n0);
         } else {
-          tma_load_2d(a_dst, &mapA2, bar_full(s), (kb - nkb1) * BK, m0);
-          tma_load_2d(b_dst, &mapB2, bar_full(s), (kb - nkb1) * BK, n0);
+          tma_load_2d(a_dst, &mapA2, bar_full(s), (kb - nkb1) * KB, m0);
+          tma_load_2d(b_dst, &mapB2, bar_full(s), (kb - nkb1) * KB, n0);
         }
         ++issued;
       }
@@ -160,8 +162,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       bool ok = true;
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % STAGES, r = kb / STAGES;
-        const int ci = kb / kChunk, buf = ci & 1;
-        if (kb % kChunk == 0 && ci >= 2) {      // the accumulator's previous chunk must have been collected
+        const int ci = kb / kChunkBlocks, buf = ci & 1;
+        if (kb % kChunkBlocks == 0 && ci >= 2) {      // the accumulator's previous chunk must have been collected
           ok = mbar_wait(bar_acc_empty(buf), ((ci >> 1) - 1) & 1, p.err, 6);
           if (!ok) break;
           tc_fence_after();
@@ -173,16 +175,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const uint32_t a_raw = base + s * S::kStageBytes, b_raw = a_raw + S::kABytes;
         const uint32_t a_lo = a_raw + S::kRawBytes, b_lo = b_raw + S::kRawBytes;
 #pragma unroll
-        for (int kk = 0; kk < BK / 8; ++kk) {
-          const uint64_t da = smem_desc_sw128(a_raw + kk * 32), db = smem_desc_sw128(b_raw + kk * 32);
-          mma_tf32(tmem_d, da, db, idesc, ((kb % kChunk) | kk) != 0);
+        for (int kk = 0; kk < KB / 8; ++kk) {
+          const uint64_t da = smem_desc_k<KB>(a_raw + kk * 32), db = smem_desc_k<KB>(b_raw + kk * 32);
+          mma_tf32(tmem_d, da, db, idesc, ((kb % kChunkBlocks) | kk) != 0);
           if (SPLIT) {
-            mma_tf32(tmem_d, smem_desc_sw128(a_lo + kk * 32), db, idesc, 1);
-            mma_tf32(tmem_d, da, smem_desc_sw128(b_lo + kk * 32), idesc, 1);
+            mma_tf32(tmem_d, smem_desc_k<KB>(a_lo + kk * 32), db, idesc, 1);
+            mma_tf32(tmem_d, da, smem_desc_k<KB>(b_lo + kk * 32), idesc, 1);
           }
         }
         mma_commit(bar_empty(s));
-        if (kb % kChunk == kChunk - 1 || kb == nkb - 1) mma_commit(bar_acc_full(buf));
+        if (kb % kChunkBlocks == kChunkBlocks - 1 || kb == nkb - 1) mma_commit(bar_acc_full(buf));
       }
     }
   } else {
@@ -240,7 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       }
       // one k-block into chunk ci the previous chunk has been multiplied: collect it now, while
       // the tensor core works on the blocks already split
-      if (kb % kChunk == 1 && kb > kChunk) {
+      if (kb % kChunkBlocks == 1 && kb > kChunkBlocks) {
         ok = collect(collected);
         ++collected;
       }
@@ -586,7 +588,7 @@ EncodeFn encode_fn() {
 // 2-D f32 row-major tensor [rows, cols] (cols contiguous), box [box_rows, box_cols], 128-byte swizzle
 // (box_cols = 32) or none.
 bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
-              uint32_t box_cols, bool swizzle = true) {
+              uint32_t box_cols, int swizzle_bytes) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {cols, rows};
@@ -594,7 +596,9 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, u
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t elem[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_INTERLEAVE_NONE,
+            swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                 : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -611,15 +615,18 @@ std::map<seeml_b200_ctx*, TcState>& states() {
   return s;
 }
 
-// Default: a swizzled K-major tile 32 elements wide; box_cols != 0 asks for an unswizzled tile of
-// that width (operands stored with the reduction index on rows).
+// Default: a swizzled K-major tile 32 elements (128 bytes) wide; box_cols = 16 is the 64-byte
+// swizzled half-width tile; any other box_cols asks for an unswizzled tile of that width
+// (operands stored with the reduction index on rows) - pass unswizzled = true for those.
 const CUtensorMap* cached_map(TcState& st, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                              uint32_t box_cols = 0) {
-  const auto key = std::make_tuple(ptr, rows, cols, box_rows, box_cols);
+                              uint32_t box_cols = 0, bool unswizzled = false) {
+  const uint32_t tag = unswizzled ? (box_cols | 0x10000u) : box_cols;
+  const auto key = std::make_tuple(ptr, rows, cols, box_rows, tag);
   auto it = st.maps.find(key);
   if (it != st.maps.end()) return &it->second;
   CUtensorMap m;
-  if (!make_map(&m, ptr, rows, cols, box_rows, box_cols ? box_cols : 32, box_cols == 0)) return nullptr;
+  const int swz = unswizzled ? 0 : (box_cols == 16 ? 64 : 128);
+  if (!make_map(&m, ptr, rows, cols, box_rows, box_cols ? box_cols : 32, swz)) return nullptr;
   return &st.maps.emplace(key, m).first->second;
 }
 
@@ -636,10 +643,10 @@ bool gemm_tc_shape_ok(const seeml_b200_ctx* c, uint64_t M, uint64_t N, uint64_t 
 
 namespace {
 
-template <int BN, bool SPLIT, int STAGES>
+template <int BN, bool SPLIT, int STAGES, int KB = BK>
 int launch_tc(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
-  using S = Smem<BN, SPLIT, STAGES>;
-  auto kern = gemm_tc_kernel<BN, SPLIT, STAGES>;
+  using S = Smem<BN, SPLIT, STAGES, KB>;
+  auto kern = gemm_tc_kernel<BN, SPLIT, STAGES, KB>;
   static bool attr_done = false;
   if (!attr_done) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) {
@@ -648,11 +655,12 @@ int launch_tc(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
     }
     attr_done = true;
   }
-  const CUtensorMap* ma = cached_map(st, g.A, g.M, g.K, BM);
-  const CUtensorMap* mb = cached_map(st, g.Bt, g.N, g.K, BN);
+  constexpr uint32_t kw = KB == BK ? 0 : KB;
+  const CUtensorMap* ma = cached_map(st, g.A, g.M, g.K, BM, kw);
+  const CUtensorMap* mb = cached_map(st, g.Bt, g.N, g.K, BN, kw);
   const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
-  const CUtensorMap* ma2 = g.K2 ? cached_map(st, g.A2, g.M, g.K2, BM) : ma;
-  const CUtensorMap* mb2 = g.K2 ? cached_map(st, g.B2t, g.N, g.K2, BN) : mb;
+  const CUtensorMap* ma2 = g.K2 ? cached_map(st, g.A2, g.M, g.K2, BM, kw) : ma;
+  const CUtensorMap* mb2 = g.K2 ? cached_map(st, g.B2t, g.N, g.K2, BN, kw) : mb;
   if (!ma || !mb || !mc || !ma2 || !mb2) return -1;
   TcParams p{(int)g.M, (int)g.N, (int)g.K, (int)g.K2, g.bias, g.addend, g.act, g.alpha == 0.0f ? 1.0f : g.alpha, st.err_dev};
   dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((g.M + BM - 1) / BM));
@@ -689,7 +697,9 @@ int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g) {
   if (!st || !st->usable || !st->err_dev) return 0;
   const bool split = c->gemm_kind == SEEML_B200_GEMM_TF32X3;
   int r;
-  if (g.N >= 192) r = split ? launch_tc<256, true, 2>(c, *st, g) : launch_tc<256, false, 4>(c, *st, g);
+  static const bool half_blocks = [] { const char* e = std::getenv("SEEML_B200_GEMM_KB"); return e && std::atoi(e) == 16; }();
+  if (g.N >= 192 && split && half_blocks) r = launch_tc<256, true, 4, 16>(c, *st, g);
+  else if (g.N >= 192) r = split ? launch_tc<256, true, 2>(c, *st, g) : launch_tc<256, false, 4>(c, *st, g);
   else r = split ? launch_tc<128, true, 3>(c, *st, g) : launch_tc<128, false, 6>(c, *st, g);
   if (r < 0) {   // tensor maps / attributes unavailable: leave the CUDA-core path in charge
     st->usable = false;
@@ -711,8 +721,8 @@ int launch_bg(seeml_b200_ctx* c, TcState& st, const TcBatched& g) {
     }
     attr_done = true;
   }
-  const CUtensorMap* ma = TA ? cached_map(st, g.A, g.a_rows, g.a_cols, BK, BM) : cached_map(st, g.A, g.a_rows, g.a_cols, BM);
-  const CUtensorMap* mb = TB ? cached_map(st, g.B, g.b_rows, g.b_cols, BK, BN) : cached_map(st, g.B, g.b_rows, g.b_cols, BN);
+  const CUtensorMap* ma = TA ? cached_map(st, g.A, g.a_rows, g.a_cols, BK, BM, true) : cached_map(st, g.A, g.a_rows, g.a_cols, BM);
+  const CUtensorMap* mb = TB ? cached_map(st, g.B, g.b_rows, g.b_cols, BK, BN, true) : cached_map(st, g.B, g.b_rows, g.b_cols, BN);
   const CUtensorMap* mc = cached_map(st, g.C, g.c_rows, g.c_cols, 32);
   if (!ma || !mb || !mc) return -1;
   BgParams p{};

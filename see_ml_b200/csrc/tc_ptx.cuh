@@ -121,6 +121,21 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
   d |= (uint64_t)2 << 61;
   return d;
 }
+// The same for tiles whose rows are one 64-byte swizzle atom wide (16 f32 of K per row):
+// 8-row groups 512 bytes apart, layout type 4 (64-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t addr) {
+  uint64_t d = (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;
+  return d;
+}
+template <int KB>
+__device__ __forceinline__ uint64_t smem_desc_k(uint32_t addr) {
+  if constexpr (KB == 32) return smem_desc_sw128(addr);
+  else return smem_desc_sw64(addr);
+}
 // Instruction descriptor, kind::tf32: D = f32 [4,6)=1, A = B = tf32 [7,10)=[10,13)=2,
 // both operands K-major (bits 15, 16 = 0), N>>3 at [17,23), M>>4 at [24,29).
 __host__ __device__ constexpr uint32_t idesc_tf32(int m, int n) {
