@@ -304,9 +304,13 @@ int dispatch(Exec& x, const Instr& ins) {
       s.sCb0 = (long long)(H * S * S); s.sCb1 = (long long)(S * S);
       s.alpha = 1.0f / std::sqrt(static_cast<float>(dh));
       s.causal = 1;
-      if (attn_tc(c, 0, s.A, s.B, P, B, S, H, dh, s.alpha) == 1) n += 1;
-      else n += k::gemm_simt(s, nullptr, st);
-      n += k::causal_softmax_rows(P, B * H, S, st);
+      if (attn_scores_softmax_tc(c, s.A, s.B, P, B, S, H, dh, s.alpha) == 1) {
+        n += 1;
+      } else {
+        if (attn_tc(c, 0, s.A, s.B, P, B, S, H, dh, s.alpha) == 1) n += 1;
+        else n += k::gemm_simt(s, nullptr, st);
+        n += k::causal_softmax_rows(P, B * H, S, st);
+      }
       k::GemmDesc pv = attn_desc(B, S, H, dh);
       pv.A = P; pv.B = x.R(in[2]); pv.C = x.W(in[3]);
       pv.M = (int)S; pv.N = (int)dh; pv.K = (int)S;

@@ -62,6 +62,9 @@ struct TcBatched {
   float alpha;
 };
 int gemm_tc_batched(seeml_b200_ctx* c, const TcBatched& g);
+// Attention forward scores + causal row softmax in one kernel (head width 64, S <= 512).
+int attn_scores_softmax_tc(seeml_b200_ctx* c, const float* Q, const float* K, float* P, uint64_t B, uint64_t S,
+                           uint64_t H, uint64_t dh, float alpha);
 // Rank-r (LoRA factor) products on the tensor cores; each returns 1 when launched, 0 when the
 // shape is not eligible. rank_n: out[M,n] = alpha A[M,K] Bnk[n,K]^T. rank_tn: per-chunk partial
 // sums partial[chunk][big][small] of W[T,big]^T S[T,small] over chunk_rows rows each.

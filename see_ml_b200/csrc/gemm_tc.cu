@@ -553,6 +553,251 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// ------------------------------------------ attention forward: scores + causal softmax -> P
+// One CTA owns 128 query rows of one (batch item, head): the scaled scores of those rows
+// against every key up to the diagonal, (i + 1) * 128 columns, accumulate in TMEM (all 512
+// columns at S = 512) and the causal row softmax runs on them in place, so the raw scores
+// never touch global memory. Sixteen worker warps share the softmax: a warp can read only
+// its own quarter of the TMEM lanes (32 query rows), so four warps serve each quarter and
+// take every fourth 64-column chunk; per-row maxima and sums of exponentials are combined
+// through shared memory in a fixed order (sums: f32 within a chunk, f64 across chunks).
+// Needs head width 64 and S <= 512, S % 128 == 0.
+struct AfParams {
+  int S, H;
+  float alpha;
+  int qx[2], qy[2];        // TMA origin of Q / K windows per batch item and head (column, row)
+  int x3;
+  int* err;
+};
+constexpr int kAfWorkers = 512;
+constexpr int kAfThreads = 64 + kAfWorkers;
+
+__device__ __forceinline__ void worker_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kAfWorkers) : "memory"); }
+
+__global__ void __launch_bounds__(kAfThreads, 1)
+attn_scores_softmax_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                           const __grid_constant__ CUtensorMap mapP, AfParams p) {
+  constexpr int kTile = BM * BK * 4;                 // one 128 x 32 f32 tile: 16 KiB
+  constexpr int kQ = 4 * kTile;                      // raw[2], lo[2]
+  constexpr int kStage = 4 * kTile;                  // a 128-key tile: raw[2], lo[2]
+  constexpr int kRed = 4 * 128 * 12;                 // per (column group, row): max f32 + sum f64
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + kQ + 2 * kStage + kRed;
+  const uint32_t q_full = bars, q_split = bars + 8, accum = bars + 16;
+  auto k_full = [&](int s) { return bars + 24u + 8u * s; };
+  auto k_split = [&](int s) { return bars + 40u + 8u * s; };
+  auto k_empty = [&](int s) { return bars + 56u + 8u * s; };
+  const uint32_t tmem_slot = bars + 72;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + kQ + 2 * kStage + kRed + 72);
+  double* red_den = reinterpret_cast<double*>(base_ptr + kQ + 2 * kStage);          // [4][128]
+  float* red_max = reinterpret_cast<float*>(base_ptr + kQ + 2 * kStage + 4 * 128 * 8);  // [4][128]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt = blockIdx.x, m0 = mt * BM, z = blockIdx.y;
+  const int bi = z / p.H, hd = z % p.H;
+  const int ntiles = mt + 1;                         // key tiles up to and including the diagonal
+  const int x0 = bi * p.qx[0] + hd * p.qx[1], y0 = bi * p.qy[0] + hd * p.qy[1];
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(q_split, kAfWorkers);
+    mbar_init(accum, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full(s), 1);
+      mbar_init(k_split(s), kAfWorkers);
+      mbar_init(k_empty(s), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * kTile);
+      tma_load_2d(base, &mapQ, q_full, x0, y0 + m0);
+      tma_load_2d(base + kTile, &mapQ, q_full, x0 + BK, y0 + m0);
+      bool ok = true;
+      int issued = 0;
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int s = j & 1, r = j >> 1;
+        if (r > 0) ok = mbar_wait(k_empty(s), (r - 1) & 1, p.err, 21);
+        if (!ok) break;
+        const uint32_t dst = base + kQ + s * kStage;
+        mbar_expect_tx(k_full(s), 2 * kTile);
+        tma_load_2d(dst, &mapK, k_full(s), x0, y0 + j * BM);
+        tma_load_2d(dst + kTile, &mapK, k_full(s), x0 + BK, y0 + j * BM);
+        ++issued;
+      }
+      if (!ok) {
+        mbar_wait(q_full, 0, p.err, 25);
+        for (int j = (issued > 2 ? issued - 2 : 0); j < issued; ++j) mbar_wait(k_full(j & 1), (j >> 1) & 1, p.err, 25);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_tf32(BM, 128);
+      bool ok = mbar_wait(q_split, 0, p.err, 22);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int s = j & 1, r = j >> 1;
+        ok = mbar_wait(k_split(s), r & 1, p.err, 22);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t kb0 = base + kQ + s * kStage;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+#pragma unroll
+          for (int kk = 0; kk < BK / 8; ++kk) {
+            const uint64_t da = smem_desc_sw128(base + kb * kTile + kk * 32);
+            const uint64_t db = smem_desc_sw128(kb0 + kb * kTile + kk * 32);
+            mma_tf32(tmem_base + j * 128, da, db, idesc, (kb | kk) != 0);
+            if (p.x3) {
+              mma_tf32(tmem_base + j * 128, smem_desc_sw128(base + (2 + kb) * kTile + kk * 32), db, idesc, 1);
+              mma_tf32(tmem_base + j * 128, da, smem_desc_sw128(kb0 + (2 + kb) * kTile + kk * 32), idesc, 1);
+            }
+          }
+        }
+        mma_commit(k_empty(s));
+      }
+      if (ok) mma_commit(accum);
+    }
+  } else {
+    const int t = threadIdx.x - 64;
+    auto split512 = [&](uint8_t* raw) {            // 32 KiB of f32 -> lo parts, 32 KiB further on
+      const float4* r = reinterpret_cast<const float4*>(raw);
+      float4* l = reinterpret_cast<float4*>(raw + 2 * kTile);
+#pragma unroll
+      for (int i = t; i < 2 * kTile / 16; i += kAfWorkers) {
+        const float4 v = r[i];
+        l[i] = make_float4(lo_part(v.x), lo_part(v.y), lo_part(v.z), lo_part(v.w));
+      }
+    };
+    bool ok = mbar_wait(q_full, 0, p.err, 23);
+    if (ok) {
+      split512(base_ptr);
+      fence_async_smem();
+      mbar_arrive(q_split);
+    }
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int s = j & 1, r = j >> 1;
+      ok = mbar_wait(k_full(s), r & 1, p.err, 23);
+      if (!ok) break;
+      split512(base_ptr + kQ + s * kStage);
+      fence_async_smem();
+      mbar_arrive(k_split(s));
+    }
+    if (ok) ok = mbar_wait(accum, 0, p.err, 24);
+    tc_fence_after();
+    // a failed wait is failed for every worker (same barriers, same limit): no one is left at
+    // the worker barrier below
+    if (ok) {
+      const int q = warp & 3, grp = (warp - 2) >> 2, row0 = q * 32;
+      const int rl = row0 + lane;                     // row within the tile
+      const int m = m0 + rl;                          // query row in the sequence; keys 0..m are visible
+      const uint32_t trow = tmem_base + ((uint32_t)row0 << 16);
+      const int nch = ntiles * 2;                     // 64-column chunks holding scores
+      auto ld64 = [&](int c, uint32_t* r) {
+        tmem_ld32(trow + c * 64, r);
+        tmem_ld32(trow + c * 64 + 32, r + 32);
+        tmem_ld_wait();
+      };
+      float mx = -INFINITY;
+      for (int c = grp; c < nch; c += 4) {
+        uint32_t r[64];
+        ld64(c, r);
+        // value selects, not branches: the 64 elements stay independent for the scheduler
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const float v = p.alpha * __uint_as_float(r[j]);
+          m4[j & 3] = fmaxf(m4[j & 3], (c * 64 + j <= m) ? v : -INFINITY);
+        }
+        mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+      }
+      red_max[grp * 128 + rl] = mx;
+      worker_sync();
+      mx = fmaxf(fmaxf(red_max[rl], red_max[128 + rl]), fmaxf(red_max[256 + rl], red_max[384 + rl]));
+      double den = 0.0;
+      for (int c = grp; c < nch; c += 4) {
+        uint32_t r[64];
+        ld64(c, r);
+        float part = 0.0f;                            // 64 terms in f32, in column order
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const float e = __expf(p.alpha * __uint_as_float(r[j]) - mx);
+          part += (c * 64 + j <= m) ? e : 0.0f;
+        }
+        den += (double)part;
+      }
+      red_den[grp * 128 + rl] = den;
+      worker_sync();
+      den = ((red_den[rl] + red_den[128 + rl]) + red_den[256 + rl]) + red_den[384 + rl];
+      const float inv = 1.0f / (float)den;
+      // every product has retired: the operand buffers serve as store staging, two 32x32 boxes
+      // per warp, plus one box of zeros per row quarter for the masked tail of the rows
+      const uint32_t ring = base + (warp - 2) * (2 * 4096);
+      uint8_t* ring_ptr = base_ptr + (warp - 2) * (2 * 4096);
+      const int prow0 = z * p.S + m0 + row0;          // first row of this warp's boxes in P [B*H*S, S]
+      bool first = true;
+      for (int c = grp; c < nch; c += 4) {
+        uint32_t r[64];
+        ld64(c, r);
+        if (!first) {
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+        }
+        first = false;
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+          uint8_t* box = ring_ptr + hb * 4096;
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            float v[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int col = c * 64 + hb * 32 + j4 * 4 + e;
+              const float pe = __expf(p.alpha * __uint_as_float(r[hb * 32 + j4 * 4 + e]) - mx) * inv;
+              v[e] = col <= m ? pe : 0.0f;
+            }
+            *reinterpret_cast<float4*>(box + lane * 128 + ((j4 ^ (lane & 7)) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+          }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&mapP, ring, c * 64, prow0);
+          tma_store_2d(&mapP, ring + 4096, c * 64 + 32, prow0);
+          tma_store_commit();
+        }
+      }
+      if (grp == 0 && nch * 64 < p.S) {
+        const uint32_t zoff = 16 * 2 * 4096 + q * 4096;
+        uint8_t* zbox = base_ptr + zoff;
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) *reinterpret_cast<float4*>(zbox + lane * 128 + (j4 << 4)) = make_float4(0.f, 0.f, 0.f, 0.f);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          for (int col = nch * 64; col < p.S; col += 32) tma_store_2d(&mapP, base + zoff, col, prow0);
+          tma_store_commit();
+        }
+      }
+      if (lane == 0) tma_store_wait_all();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
 // [K,N] row-major -> [N,K] row-major (one-time copy of a frozen weight).
 __global__ void transpose_kernel(const float* __restrict__ in, float* __restrict__ out, int K, int N) {
   __shared__ float tile[32][33];
@@ -845,6 +1090,40 @@ int gemm_tc_rank_tn(seeml_b200_ctx* c, const float* W, const float* S, float* pa
     st->usable = false;
     return 0;
   }
+  return 1;
+}
+
+// Scores + causal softmax of attention forward in one kernel: P[z, i, :] = softmax over the
+// visible keys of alpha * Q_z[i] . K_z[j]. Q and K are [B*S, H*64]. 1 = launched, 0 = not eligible.
+int attn_scores_softmax_tc(seeml_b200_ctx* c, const float* Q, const float* K, float* P, uint64_t B, uint64_t S,
+                           uint64_t H, uint64_t dh, float alpha) {
+  if (c->gemm_kind != SEEML_B200_GEMM_TF32X3 && c->gemm_kind != SEEML_B200_GEMM_TF32) return 0;
+  if (dh != 64 || S % BM != 0 || S > 512 || B * H == 0 || B * H > 65535) return 0;
+  if ((B * S) >> 31 || (H * dh) >> 31 || (B * H * S) >> 31) return 0;
+  if ((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(P)) & 15) return 0;
+  TcState* st = state_of(c, false);
+  if (!st || !st->usable || !st->err_dev) return 0;
+  constexpr int kSmem = 12 * BM * BK * 4 + 4 * 128 * 12 + 256 + 1024;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(attn_scores_softmax_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      st->usable = false;
+      return 0;
+    }
+    attr_done = true;
+  }
+  const CUtensorMap* mq = cached_map(*st, Q, B * S, H * dh, BM);
+  const CUtensorMap* mk = cached_map(*st, K, B * S, H * dh, BM);
+  const CUtensorMap* mp = cached_map(*st, P, B * H * S, S, 32);
+  if (!mq || !mk || !mp) return 0;
+  AfParams p{};
+  p.S = (int)S; p.H = (int)H; p.alpha = alpha;
+  p.qx[0] = 0; p.qx[1] = (int)dh; p.qy[0] = (int)S; p.qy[1] = 0;
+  p.x3 = c->gemm_kind == SEEML_B200_GEMM_TF32X3; p.err = st->err_dev;
+  dim3 grid((unsigned)(S / BM), (unsigned)(B * H));
+  attn_scores_softmax_kernel<<<grid, kAfThreads, kSmem, c->stream>>>(*mq, *mk, *mp, p);
   return 1;
 }
 
