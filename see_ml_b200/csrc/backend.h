@@ -65,6 +65,10 @@ int gemm_tc_batched(seeml_b200_ctx* c, const TcBatched& g);
 // Attention forward scores + causal row softmax in one kernel (head width 64, S <= 512).
 int attn_scores_softmax_tc(seeml_b200_ctx* c, const float* Q, const float* K, float* P, uint64_t B, uint64_t S,
                            uint64_t H, uint64_t dh, float alpha);
+// Backward: dS = P * (dP - rowsum(dP * P)) with dP = dO V^T kept in TMEM (same shape limits).
+bool attn_rows_eligible(const seeml_b200_ctx* c, uint64_t B, uint64_t S, uint64_t H, uint64_t dh);
+int attn_ds_tc(seeml_b200_ctx* c, const float* dO, const float* V, const float* P, float* dS, uint64_t B, uint64_t S,
+               uint64_t H, uint64_t dh);
 // Rank-r (LoRA factor) products on the tensor cores; each returns 1 when launched, 0 when the
 // shape is not eligible. rank_n: out[M,n] = alpha A[M,K] Bnk[n,K]^T. rank_tn: per-chunk partial
 // sums partial[chunk][big][small] of W[T,big]^T S[T,small] over chunk_rows rows each.
@@ -80,7 +84,7 @@ const float* gemm_tc_transposed_weight(seeml_b200_ctx* c, uint64_t rodata_off, u
 
 // A group of consecutive instructions executed by fewer, fused kernels (FUSED mode).
 struct FusedStep {
-  enum Kind { kLoraFwd = 1, kLoraBwd = 2, kDgradAdd = 3, kSwigluFwd = 4, kSwigluBwd = 5 } kind;
+  enum Kind { kLoraFwd = 1, kLoraBwd = 2, kDgradAdd = 3, kAttnDs = 4, kSwigluFwd = 5, kSwigluBwd = 6 } kind;
   uint32_t first = 0, count = 0;
   uint32_t idx[8] = {0, 0, 0, 0, 0, 0, 0, 0};   // instruction indices of the group's members by role
   float alpha = 1.0f;

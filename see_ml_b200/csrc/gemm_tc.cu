@@ -566,6 +566,7 @@ struct AfParams {
   int S, H;
   float alpha;
   int qx[2], qy[2];        // TMA origin of Q / K windows per batch item and head (column, row)
+  const float* pin;        // MODE 1: the probabilities P [B*H*S, S] saved by the forward pass
   int x3;
   int* err;
 };
@@ -574,6 +575,10 @@ constexpr int kAfThreads = 64 + kAfWorkers;
 
 __device__ __forceinline__ void worker_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kAfWorkers) : "memory"); }
 
+// MODE 0: A = Q, B = K, output P = causal softmax(alpha A B^T).
+// MODE 1 (backward): A = dO, B = V, so TMEM holds dP = dO V^T; output dS = P * (dP - rowsum(dP * P))
+// with P read from global memory - dP itself is never written.
+template <int MODE>
 __global__ void __launch_bounds__(kAfThreads, 1)
 attn_scores_softmax_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                            const __grid_constant__ CUtensorMap mapP, AfParams p) {
@@ -694,6 +699,15 @@ attn_scores_softmax_kernel(const __grid_constant__ CUtensorMap mapQ, const __gri
       fence_async_smem();
       mbar_arrive(k_split(s));
     }
+    if (MODE == 1 && ok) {
+      // while the last products run: pull this tile's block of P toward L2 (one 128-byte line per request)
+      const int lines_per_row = ntiles * 4;
+      const char* pbase = reinterpret_cast<const char*>(p.pin + ((size_t)z * p.S + m0) * p.S);
+      for (int i = t; i < BM * lines_per_row; i += kAfWorkers) {
+        const char* a = pbase + (size_t)(i / lines_per_row) * p.S * 4 + (size_t)(i % lines_per_row) * 128;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+      }
+    }
     if (ok) ok = mbar_wait(accum, 0, p.err, 24);
     tc_fence_after();
     // a failed wait is failed for every worker (same barriers, same limit): no one is left at
@@ -709,7 +723,34 @@ attn_scores_softmax_kernel(const __grid_constant__ CUtensorMap mapQ, const __gri
         tmem_ld32(trow + c * 64 + 32, r + 32);
         tmem_ld_wait();
       };
-      float mx = -INFINITY;
+      float mx = 0.0f, inv = 1.0f, rsum = 0.0f;
+      // two 32x32 boxes per warp (one 64-column chunk of its 32 rows), in the layout of a TMA
+      // store box: row * 128 bytes, 16-byte chunk k of a row at position k ^ (row & 7)
+      const uint32_t ring = base + (warp - 2) * (2 * 4096);
+      uint8_t* ring_ptr = base_ptr + (warp - 2) * (2 * 4096);
+      const int prow0 = z * p.S + m0 + row0;          // first row of this warp's boxes in P [B*H*S, S]
+      // MODE 1: bring the warp's 32 x 64 block of P into its boxes with row-wise coalesced loads
+      // (every product has retired by now, so the operand buffers are free)
+      auto load_p_chunk = [&](int c) {
+        const float* src = p.pin + (size_t)prow0 * p.S + c * 64 + lane * 2;
+        uint8_t* dst = ring_ptr + (lane >> 4) * 4096 + (lane & 1) * 8;
+        const int ch = (lane & 15) >> 1;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {       // 16 row loads in flight at a time
+          float2 v2[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            v2[i] = __ldg(reinterpret_cast<const float2*>(src + (size_t)(half * 16 + i) * p.S));
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int rr = half * 16 + i;
+            *reinterpret_cast<float2*>(dst + rr * 128 + ((ch ^ (rr & 7)) << 4)) = v2[i];
+          }
+        }
+        __syncwarp();
+      };
+      if constexpr (MODE == 0) {
+      mx = -INFINITY;
       for (int c = grp; c < nch; c += 4) {
         uint32_t r[64];
         ld64(c, r);
@@ -740,31 +781,61 @@ attn_scores_softmax_kernel(const __grid_constant__ CUtensorMap mapQ, const __gri
       red_den[grp * 128 + rl] = den;
       worker_sync();
       den = ((red_den[rl] + red_den[128 + rl]) + red_den[256 + rl]) + red_den[384 + rl];
-      const float inv = 1.0f / (float)den;
+      inv = 1.0f / (float)den;
+      } else {
+        // rowsum(dP * P): P is zero beyond the diagonal, so no mask is needed here
+        double dot = 0.0;
+        for (int c = grp; c < nch; c += 4) {
+          load_p_chunk(c);
+          uint32_t r[64];
+          ld64(c, r);
+          float d4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int j4 = 0; j4 < 16; ++j4) {
+            const float4 pv = *reinterpret_cast<const float4*>(ring_ptr + (j4 >> 3) * 4096 + lane * 128 +
+                                                               (((j4 & 7) ^ (lane & 7)) << 4));
+            d4[0] = fmaf(__uint_as_float(r[j4 * 4 + 0]), pv.x, d4[0]);
+            d4[1] = fmaf(__uint_as_float(r[j4 * 4 + 1]), pv.y, d4[1]);
+            d4[2] = fmaf(__uint_as_float(r[j4 * 4 + 2]), pv.z, d4[2]);
+            d4[3] = fmaf(__uint_as_float(r[j4 * 4 + 3]), pv.w, d4[3]);
+          }
+          dot += (double)((d4[0] + d4[1]) + (d4[2] + d4[3]));
+          __syncwarp();                                // the boxes are refilled by the next chunk
+        }
+        red_den[grp * 128 + rl] = dot;
+        worker_sync();
+        dot = ((red_den[rl] + red_den[128 + rl]) + red_den[256 + rl]) + red_den[384 + rl];
+        rsum = (float)dot;
+      }
       // every product has retired: the operand buffers serve as store staging, two 32x32 boxes
       // per warp, plus one box of zeros per row quarter for the masked tail of the rows
-      const uint32_t ring = base + (warp - 2) * (2 * 4096);
-      uint8_t* ring_ptr = base_ptr + (warp - 2) * (2 * 4096);
-      const int prow0 = z * p.S + m0 + row0;          // first row of this warp's boxes in P [B*H*S, S]
       bool first = true;
       for (int c = grp; c < nch; c += 4) {
-        uint32_t r[64];
-        ld64(c, r);
         if (!first) {
           if (lane == 0) tma_store_wait_read();
           __syncwarp();
         }
         first = false;
+        if constexpr (MODE == 1) load_p_chunk(c);
+        uint32_t r[64];
+        ld64(c, r);
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {
           uint8_t* box = ring_ptr + hb * 4096;
 #pragma unroll
           for (int j4 = 0; j4 < 8; ++j4) {
             float v[4];
+            float pq[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (MODE == 1) {   // the dS values replace the P values they were made from
+              const float4 pv = *reinterpret_cast<const float4*>(box + lane * 128 + ((j4 ^ (lane & 7)) << 4));
+              pq[0] = pv.x; pq[1] = pv.y; pq[2] = pv.z; pq[3] = pv.w;
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int col = c * 64 + hb * 32 + j4 * 4 + e;
-              const float pe = __expf(p.alpha * __uint_as_float(r[hb * 32 + j4 * 4 + e]) - mx) * inv;
+              float pe;
+              if constexpr (MODE == 0) pe = __expf(p.alpha * __uint_as_float(r[hb * 32 + j4 * 4 + e]) - mx) * inv;
+              else pe = pq[e] * (__uint_as_float(r[hb * 32 + j4 * 4 + e]) - rsum);
               v[e] = col <= m ? pe : 0.0f;
             }
             *reinterpret_cast<float4*>(box + lane * 128 + ((j4 ^ (lane & 7)) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
@@ -1093,38 +1164,56 @@ int gemm_tc_rank_tn(seeml_b200_ctx* c, const float* W, const float* S, float* pa
   return 1;
 }
 
-// Scores + causal softmax of attention forward in one kernel: P[z, i, :] = softmax over the
-// visible keys of alpha * Q_z[i] . K_z[j]. Q and K are [B*S, H*64]. 1 = launched, 0 = not eligible.
-int attn_scores_softmax_tc(seeml_b200_ctx* c, const float* Q, const float* K, float* P, uint64_t B, uint64_t S,
-                           uint64_t H, uint64_t dh, float alpha) {
+// Attention's score-shaped products with their row softmax in one kernel (head width 64,
+// S <= 512, S % 128 == 0). mode 0: P[z,i,:] = softmax over the visible keys of alpha A_z[i].B_z[j]
+// (A = Q, B = K). mode 1: out = Pin * (dP - rowsum(dP * Pin)) with dP = A B^T (A = dO, B = V).
+// A and B are [B*S, H*64]; out / Pin are [B*H*S, S]. 1 = launched, 0 = not eligible.
+static int attn_rows_launch(seeml_b200_ctx* c, int mode, const float* A, const float* Bm, const float* Pin, float* out,
+                            uint64_t B, uint64_t S, uint64_t H, uint64_t dh, float alpha) {
   if (c->gemm_kind != SEEML_B200_GEMM_TF32X3 && c->gemm_kind != SEEML_B200_GEMM_TF32) return 0;
   if (dh != 64 || S % BM != 0 || S > 512 || B * H == 0 || B * H > 65535) return 0;
   if ((B * S) >> 31 || (H * dh) >> 31 || (B * H * S) >> 31) return 0;
-  if ((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(P)) & 15) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bm) | reinterpret_cast<uintptr_t>(out) |
+       reinterpret_cast<uintptr_t>(Pin)) & 15)
+    return 0;
   TcState* st = state_of(c, false);
   if (!st || !st->usable || !st->err_dev) return 0;
   constexpr int kSmem = 12 * BM * BK * 4 + 4 * 128 * 12 + 256 + 1024;
   static bool attr_done = false;
   if (!attr_done) {
-    if (cudaFuncSetAttribute(attn_scores_softmax_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
-        cudaSuccess) {
+    if (cudaFuncSetAttribute(attn_scores_softmax_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_scores_softmax_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
       cudaGetLastError();
       st->usable = false;
       return 0;
     }
     attr_done = true;
   }
-  const CUtensorMap* mq = cached_map(*st, Q, B * S, H * dh, BM);
-  const CUtensorMap* mk = cached_map(*st, K, B * S, H * dh, BM);
-  const CUtensorMap* mp = cached_map(*st, P, B * H * S, S, 32);
+  const CUtensorMap* mq = cached_map(*st, A, B * S, H * dh, BM);
+  const CUtensorMap* mk = cached_map(*st, Bm, B * S, H * dh, BM);
+  const CUtensorMap* mp = cached_map(*st, out, B * H * S, S, 32);
   if (!mq || !mk || !mp) return 0;
   AfParams p{};
   p.S = (int)S; p.H = (int)H; p.alpha = alpha;
   p.qx[0] = 0; p.qx[1] = (int)dh; p.qy[0] = (int)S; p.qy[1] = 0;
+  p.pin = Pin;
   p.x3 = c->gemm_kind == SEEML_B200_GEMM_TF32X3; p.err = st->err_dev;
   dim3 grid((unsigned)(S / BM), (unsigned)(B * H));
-  attn_scores_softmax_kernel<<<grid, kAfThreads, kSmem, c->stream>>>(*mq, *mk, *mp, p);
+  if (mode == 0) attn_scores_softmax_kernel<0><<<grid, kAfThreads, kSmem, c->stream>>>(*mq, *mk, *mp, p);
+  else attn_scores_softmax_kernel<1><<<grid, kAfThreads, kSmem, c->stream>>>(*mq, *mk, *mp, p);
   return 1;
+}
+int attn_scores_softmax_tc(seeml_b200_ctx* c, const float* Q, const float* K, float* P, uint64_t B, uint64_t S,
+                           uint64_t H, uint64_t dh, float alpha) {
+  return attn_rows_launch(c, 0, Q, K, nullptr, P, B, S, H, dh, alpha);
+}
+bool attn_rows_eligible(const seeml_b200_ctx* c, uint64_t B, uint64_t S, uint64_t H, uint64_t dh) {
+  return (c->gemm_kind == SEEML_B200_GEMM_TF32X3 || c->gemm_kind == SEEML_B200_GEMM_TF32) && dh == 64 &&
+         S % BM == 0 && S <= 512 && B * H > 0 && B * H <= 65535 && !((B * H * S) >> 31);
+}
+int attn_ds_tc(seeml_b200_ctx* c, const float* dO, const float* V, const float* P, float* dS, uint64_t B, uint64_t S,
+               uint64_t H, uint64_t dh) {
+  return attn_rows_launch(c, 1, dO, V, P, dS, B, S, H, dh, 1.0f);
 }
 
 // Transposed [N,K] copy of the frozen weight at `rodata_off` ([K,N]); made on first request.

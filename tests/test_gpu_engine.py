@@ -258,15 +258,16 @@ def test_fused_groups_match_contract_mode_and_oracle_on_tensor_core_shapes():
     """A decoder wide enough for the tensor-core GEMM and the LoRA group fusions (forward
     C' = [X|t].[W^T|aB^T]^T, backward dX = [p+][g|dt].[W|A]^T, rank-r kernels): every LoRA
     gradient and the loss after one hand-fed backward pass, fused vs one-kernel-per-
-    instruction vs the C oracle. Adapters' B factors are made nonzero so every path carries
+    instruction vs the C oracle. The geometry also takes the tensor-core attention kernels
+    (scores + softmax in TMEM forward; dS from dP held in TMEM in fused mode). Adapters' B factors are made nonzero so every path carries
     signal."""
     from see_ml_b200 import plansynth as PS
     from see_ml_b200.engine import UpdateEngine
     lib = L.lib()
     rng = np.random.default_rng(11)
-    V, D, H, Ff, S, T = 512, 256, 4, 512, 64, 512
+    V, D, H, Ff, S, T = 512, 256, 4, 512, 128, 1024     # 64-wide heads, S % 128 == 0: tensor-core attention
     model = PS.llama_decoder(V, D, H, Ff, 2, S, rng, std=0.05)
-    spec = PS.TrainSpec(batch=T, lora_rank=8, lora_alpha=16.0,
+    spec = PS.TrainSpec(batch=T, lora_rank=16, lora_alpha=32.0,
                         targets=("wq", "wk", "wv", "wo", "w_up", "w_down"))
     blob, info = PS.synthesize(model, spec, hasher=lambda b, o: int(
         lib.seeml_b200_plan_self_hash(np.frombuffer(b, np.uint8).ctypes.data, len(b), o)))
