@@ -36,7 +36,8 @@ using namespace tc;
 
 constexpr int BM = 128;
 constexpr int BK = 32;                 // f32 elements = one 128-byte swizzle row
-constexpr int kThreadsTC = 192;
+constexpr int kBgWorkers = 256;          // batched kernel: 8 split warps, the first 4 also collect and store
+constexpr int kThreadsTC = 64 + kBgWorkers;
 
 struct TcParams {
   int M, N, K;
@@ -45,6 +46,7 @@ struct TcParams {
   const float* addend;   // nullable, [M,N] row-major: C = addend + A.B^T (+ A2.B2^T)
   int act;               // 0 none 1 relu 2 gelu 3 silu
   float alpha;           // scales the product before addend / bias / activation
+  int b_lo;              // the lo tiles of B (main pair) come from a precomputed copy through mapBlo
   int* err;              // device error word
 };
 
@@ -84,7 +86,7 @@ template <int BN, bool SPLIT, int STAGES, int KB>
 __global__ void __launch_bounds__(kThreadsV2, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapA2,
-               const __grid_constant__ CUtensorMap mapB2, TcParams p) {
+               const __grid_constant__ CUtensorMap mapB2, const __grid_constant__ CUtensorMap mapBlo, TcParams p) {
   using S = Smem<BN, SPLIT, STAGES, KB>;
   constexpr int kChunkBlocks = kChunk * (BK / KB);   // k-blocks per accumulation chunk (128 elements of K)
   extern __shared__ uint8_t smem_raw[];
@@ -120,7 +122,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  // Stage layout: [A raw][A lo][B raw][B lo] (the lo tiles only when SPLIT). Narrow tiles stack
+  // B_hi and B_lo into one MMA of width 2*BN (see bgemm_tc_kernel): two MMAs per step, not three.
+  constexpr bool STACK = SPLIT && BN <= 64;
+  constexpr int kAccCols = STACK ? 2 * BN : BN;
+  constexpr int kBOff = S::kABytes * (SPLIT ? 2 : 1);
+  constexpr uint32_t kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
@@ -139,11 +146,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const int s = kb % STAGES, r = kb / STAGES;
         if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 1);
         if (!ok) break;
-        const uint32_t a_dst = base + s * S::kStageBytes, b_dst = a_dst + S::kABytes;
-        mbar_expect_tx(bar_full(s), S::kRawBytes);
+        const uint32_t a_dst = base + s * S::kStageBytes, b_dst = a_dst + kBOff;
+        const bool lo_too = SPLIT && p.b_lo && kb < nkb1;     // frozen weight: its lo tile is loaded, not derived
+        mbar_expect_tx(bar_full(s), S::kRawBytes + (lo_too ? S::kBBytes : 0));
         if (kb < nkb1) {
           tma_load_2d(a_dst, &mapA, bar_full(s), kb * KB, m0);
           tma_load_2d(b_dst, &mapB, bar_full(s), kb * KB, n0);
+          if (lo_too) tma_load_2d(b_dst + S::kBBytes, &mapBlo, bar_full(s), kb * KB, n0);
         } else {
           tma_load_2d(a_dst, &mapA2, bar_full(s), (kb - nkb1) * KB, m0);
           tma_load_2d(b_dst, &mapB2, bar_full(s), (kb - nkb1) * KB, n0);
@@ -158,7 +167,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   } else if (warp == 1) {
     // ---- MMA issuer ---------------------------------------------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = idesc_tf32(BM, BN);
+      constexpr uint32_t idesc = idesc_tf32(BM, BN), idesc2 = idesc_tf32(BM, STACK ? 2 * BN : BN);
       bool ok = true;
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % STAGES, r = kb / STAGES;
@@ -171,16 +180,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         ok = mbar_wait(SPLIT ? bar_split(s) : bar_full(s), r & 1, p.err, 2);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * BN;
-        const uint32_t a_raw = base + s * S::kStageBytes, b_raw = a_raw + S::kABytes;
-        const uint32_t a_lo = a_raw + S::kRawBytes, b_lo = b_raw + S::kRawBytes;
+        const uint32_t tmem_d = tmem_base + buf * kAccCols;
+        const uint32_t a_raw = base + s * S::kStageBytes, b_raw = a_raw + kBOff;
+        const uint32_t a_lo = a_raw + S::kABytes, b_lo = b_raw + S::kBBytes;
 #pragma unroll
         for (int kk = 0; kk < KB / 8; ++kk) {
           const uint64_t da = smem_desc_k<KB>(a_raw + kk * 32), db = smem_desc_k<KB>(b_raw + kk * 32);
-          mma_tf32(tmem_d, da, db, idesc, ((kb % kChunkBlocks) | kk) != 0);
-          if (SPLIT) {
+          if (STACK) {
+            mma_tf32(tmem_d, da, db, idesc2, ((kb % kChunkBlocks) | kk) != 0);
             mma_tf32(tmem_d, smem_desc_k<KB>(a_lo + kk * 32), db, idesc, 1);
-            mma_tf32(tmem_d, da, smem_desc_k<KB>(b_lo + kk * 32), idesc, 1);
+          } else {
+            mma_tf32(tmem_d, da, db, idesc, ((kb % kChunkBlocks) | kk) != 0);
+            if (SPLIT) {
+              mma_tf32(tmem_d, smem_desc_k<KB>(a_lo + kk * 32), db, idesc, 1);
+              mma_tf32(tmem_d, da, smem_desc_k<KB>(b_lo + kk * 32), idesc, 1);
+            }
           }
         }
         mma_commit(bar_empty(s));
@@ -209,10 +223,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 #pragma unroll
         for (int c = 0; c < NH / LD; ++c) {
           uint32_t r[32];
-          tmem_ld_cols<LD>(tmem_base + ((uint32_t)row0 << 16) + buf * BN + half * NH + c * LD, r);
+          tmem_ld_cols<LD>(tmem_base + ((uint32_t)row0 << 16) + buf * kAccCols + half * NH + c * LD, r);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]);
+          if (STACK) {
+            tmem_ld_cols<LD>(tmem_base + ((uint32_t)row0 << 16) + buf * kAccCols + BN + half * NH + c * LD, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]);
+          }
         }
       }
       tc_fence_before();
@@ -222,21 +242,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     for (int kb = 0; kb < nkb && ok; ++kb) {
       const int s = kb % STAGES, r = kb / STAGES;
       if (SPLIT) {
-        constexpr int NV = S::kRawBytes / 16;
         ok = mbar_wait(bar_full(s), r & 1, p.err, 3);
         if (!ok) break;
-        const float4* raw = reinterpret_cast<const float4*>(base_ptr + s * S::kStageBytes);
-        float4* lo = reinterpret_cast<float4*>(base_ptr + s * S::kStageBytes + S::kRawBytes);
+        uint8_t* stg = base_ptr + s * S::kStageBytes;
+        auto split_range = [&](uint8_t* raw, int bytes) {     // lo tile directly behind its raw tile
+          const float4* rp = reinterpret_cast<const float4*>(raw);
+          float4* lp = reinterpret_cast<float4*>(raw + bytes);
 #pragma unroll 4
-        for (int i = t; i < NV; i += kWorkers) {
-          const float4 v = raw[i];
-          float4 l;
-          l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
-          l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
-          l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
-          l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-          lo[i] = l;
-        }
+          for (int i = t; i < bytes / 16; i += kWorkers) {
+            const float4 v = rp[i];
+            float4 l;
+            l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+            l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+            l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+            l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+            lp[i] = l;
+          }
+        };
+        split_range(stg, S::kABytes);
+        if (!(p.b_lo && kb < nkb1)) split_range(stg + kBOff, S::kBBytes);
         fence_async_smem();
         mbar_arrive(bar_split(s));
       }
@@ -341,7 +365,7 @@ __device__ __forceinline__ void split_plain(const uint8_t* raw, uint8_t* lo, int
   const float4* r = reinterpret_cast<const float4*>(raw);
   float4* l = reinterpret_cast<float4*>(lo);
 #pragma unroll 4
-  for (int i = t; i < bytes / 16; i += 128) {
+  for (int i = t; i < bytes / 16; i += kBgWorkers) {
     const float4 v = r[i];
     l[i] = make_float4(lo_part(v.x), lo_part(v.y), lo_part(v.z), lo_part(v.w));
   }
@@ -353,7 +377,7 @@ template <int W>
 __device__ __forceinline__ void split_transposed(const uint8_t* raw, uint8_t* hi, uint8_t* lo, int t) {
   const float* r = reinterpret_cast<const float*>(raw);
 #pragma unroll 2
-  for (int i = t; i < W * 8; i += 128) {
+  for (int i = t; i < W * 8; i += kBgWorkers) {
     const int n = i % W, k4 = i / W;
     const float v0 = r[(4 * k4 + 0) * W + n], v1 = r[(4 * k4 + 1) * W + n];
     const float v2 = r[(4 * k4 + 2) * W + n], v3 = r[(4 * k4 + 3) * W + n];
@@ -393,7 +417,7 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full(s), 1);
-      mbar_init(bar_split(s), 128);
+      mbar_init(bar_split(s), kBgWorkers);
       mbar_init(bar_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -402,7 +426,12 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators, chunks alternate
+  // 3xTF32 with the hi and lo tiles of B adjacent in shared memory: one MMA of width 2*BN
+  // multiplies A_hi with [B_hi; B_lo] (columns [0,BN) and [BN,2BN) of the accumulator), a second
+  // of width BN adds A_lo.B_hi into the first half; the halves are summed when a chunk is
+  // collected. Two MMAs per step instead of three - their cost does not depend on the width.
+  constexpr int kAccCols = 2 * BN;                 // per accumulator
+  constexpr uint32_t kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;   // two accumulators, chunks alternate
   constexpr int LD = BN >= 32 ? 32 : 16;       // columns per TMEM load / store box
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -444,7 +473,7 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = idesc_tf32(BM, BN);
+      constexpr uint32_t idesc = idesc_tf32(BM, BN), idesc2 = idesc_tf32(BM, 2 * BN);
       bool ok = true;
       for (int i = 0; i < nk; ++i) {
         const int s = i % STAGES, r = i / STAGES;
@@ -457,14 +486,15 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         ok = mbar_wait(bar_split(s), r & 1, p.err, 12);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * BN;
+        const uint32_t tmem_d = tmem_base + buf * kAccCols;
 #pragma unroll
         for (int kk = 0; kk < BK / 8; ++kk) {
           const uint64_t da = smem_desc_sw128(base + a_hi(s) + kk * 32), db = smem_desc_sw128(base + b_hi(s) + kk * 32);
-          mma_tf32(tmem_d, da, db, idesc, ((i % kChunk) | kk) != 0);
           if (p.x3) {
+            mma_tf32(tmem_d, da, db, idesc2, ((i % kChunk) | kk) != 0);      // b_lo follows b_hi in the stage
             mma_tf32(tmem_d, smem_desc_sw128(base + a_lo(s) + kk * 32), db, idesc, 1);
-            mma_tf32(tmem_d, da, smem_desc_sw128(base + b_lo(s) + kk * 32), idesc, 1);
+          } else {
+            mma_tf32(tmem_d, da, db, idesc, ((i % kChunk) | kk) != 0);
           }
         }
         mma_commit(bar_empty(s));
@@ -482,17 +512,25 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
     const int nchunks = (nk + kChunk - 1) / kChunk;
     int collected = 0;
+    const bool collector = warp < 6;               // warps 2..5: one per TMEM lane quadrant
     auto collect = [&](int ci) {
+      if (!collector) return true;
       const int buf = ci & 1;
       if (!mbar_wait(bar_acc_full(buf), (ci >> 1) & 1, p.err, 14)) return false;
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < BN / LD; ++c) {
         uint32_t r[32];
-        tmem_ld_cols<LD>(tmem_base + ((uint32_t)row0 << 16) + buf * BN + c * LD, r);
+        tmem_ld_cols<LD>(tmem_base + ((uint32_t)row0 << 16) + buf * kAccCols + c * LD, r);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]);
+        if (p.x3) {
+          tmem_ld_cols<LD>(tmem_base + ((uint32_t)row0 << 16) + buf * kAccCols + BN + c * LD, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]);
+        }
       }
       tc_fence_before();
       mbar_arrive(bar_acc_empty(buf));
@@ -514,7 +552,7 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       }
     }
     for (; ok && collected < nchunks; ++collected) ok = collect(collected);
-    if (ok) {
+    if (ok && collector) {
       // every product has retired, so the first stage's buffers serve as store staging
       const uint32_t stage = base + q * 4096;
       uint8_t* stage_ptr = base_ptr + q * 4096;
@@ -869,6 +907,12 @@ attn_scores_softmax_kernel(const __grid_constant__ CUtensorMap mapQ, const __gri
   if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
+// lo part of every element: x minus x with the low 13 mantissa bits cleared (one-time, frozen weights).
+__global__ void lo_copy_kernel(const float* __restrict__ in, float* __restrict__ out, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = lo_part(in[i]);
+}
+
 // [K,N] row-major -> [N,K] row-major (one-time copy of a frozen weight).
 __global__ void transpose_kernel(const float* __restrict__ in, float* __restrict__ out, int K, int N) {
   __shared__ float tile[32][33];
@@ -924,6 +968,7 @@ struct TcState {
   bool attrs_set = false;
   bool usable = true;
   float* rank_scratch = nullptr;
+  std::map<const float*, float*> lo_copies;   // frozen B operand -> its precomputed lo part (x - tf32(x))
   std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> maps;
 };
 std::map<seeml_b200_ctx*, TcState>& states() {
@@ -977,10 +1022,17 @@ int launch_tc(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
   const CUtensorMap* ma2 = g.K2 ? cached_map(st, g.A2, g.M, g.K2, BM, kw) : ma;
   const CUtensorMap* mb2 = g.K2 ? cached_map(st, g.B2t, g.N, g.K2, BN, kw) : mb;
-  if (!ma || !mb || !mc || !ma2 || !mb2) return -1;
-  TcParams p{(int)g.M, (int)g.N, (int)g.K, (int)g.K2, g.bias, g.addend, g.act, g.alpha == 0.0f ? 1.0f : g.alpha, st.err_dev};
+  const float* blo = nullptr;
+  if (SPLIT) {
+    auto it = st.lo_copies.find(g.Bt);
+    if (it != st.lo_copies.end()) blo = it->second;
+  }
+  const CUtensorMap* mblo = blo ? cached_map(st, blo, g.N, g.K, BN, kw) : mb;
+  if (!ma || !mb || !mc || !ma2 || !mb2 || !mblo) return -1;
+  TcParams p{(int)g.M, (int)g.N, (int)g.K, (int)g.K2, g.bias, g.addend, g.act, g.alpha == 0.0f ? 1.0f : g.alpha,
+             blo != nullptr, st.err_dev};
   dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((g.M + BM - 1) / BM));
-  kern<<<grid, kThreadsV2, S::kTotal, c->stream>>>(*ma, *mb, *mc, *ma2, *mb2, p);
+  kern<<<grid, kThreadsV2, S::kTotal, c->stream>>>(*ma, *mb, *mc, *ma2, *mb2, *mblo, p);
   return 1;
 }
 
@@ -1234,6 +1286,21 @@ const float* gemm_tc_transposed_weight(seeml_b200_ctx* c, uint64_t rodata_off, u
   return t;
 }
 
+// Registers a precomputed lo copy for a frozen B operand (device pointer `w`, `elems` floats).
+static int ensure_lo_copy(seeml_b200_ctx* c, const float* w, uint64_t elems) {
+  TcState* st = state_of(c, false);
+  if (!st || c->gemm_kind != SEEML_B200_GEMM_TF32X3) return 0;
+  if (st->lo_copies.count(w)) return 0;
+  float* lo = nullptr;
+  if (cudaMalloc(&lo, elems * sizeof(float)) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;                                   // not fatal: the kernel derives the lo tiles itself
+  }
+  lo_copy_kernel<<<1184, 256, 0, c->stream>>>(w, lo, (size_t)elems);
+  st->lo_copies[w] = lo;
+  return 0;
+}
+
 static bool tc_instr(const seeml_b200_ctx* c, const Instr& ins) {
   if (ins.opcode != kGemmNN && ins.opcode != kGemmNT) return false;
   if (ins.opcode == kGemmNN && !is_rodata(ins.in[1])) return false;   // only frozen weights have a transposed copy
@@ -1244,9 +1311,13 @@ int gemm_tensor_core_prepare(seeml_b200_ctx* c, const Instr& ins) {
   if (c->gemm_kind == SEEML_B200_GEMM_FP32_SIMT || c->gemm_kind == SEEML_B200_GEMM_BF16) return 0;
   if (!state_of(c, true)) return cuda_fail(cudaGetLastError(), "tc error word");
   if (!tc_instr(c, ins)) return 0;
-  if (ins.opcode == kGemmNN &&
-      !gemm_tc_transposed_weight(c, ref_off(ins.in[1]), ins.out[2], ins.out[1], true))
-    return fail("UpdateEngine: transposed weight allocation failed");
+  if (ins.opcode == kGemmNN) {
+    const float* wt = gemm_tc_transposed_weight(c, ref_off(ins.in[1]), ins.out[2], ins.out[1], true);
+    if (!wt) return fail("UpdateEngine: transposed weight allocation failed");
+    ensure_lo_copy(c, wt, ins.out[1] * ins.out[2]);
+  } else if (is_rodata(ins.in[1])) {
+    ensure_lo_copy(c, reinterpret_cast<const float*>(c->rodata + ref_off(ins.in[1])), ins.out[1] * ins.out[2]);
+  }
   return 0;
 }
 
@@ -1287,6 +1358,7 @@ void gemm_tensor_core_release(seeml_b200_ctx* c) {
   if (sit == states().end()) return;
   cudaFree(sit->second.err_dev);
   cudaFree(sit->second.rank_scratch);
+  for (auto& kv : sit->second.lo_copies) cudaFree(kv.second);
   states().erase(sit);
 }
 
