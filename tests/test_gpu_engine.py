@@ -305,3 +305,30 @@ def test_fused_groups_match_contract_mode_and_oracle_on_tensor_core_shapes():
             ref = want[g:g + n * 4].view(np.float32)
             np.testing.assert_allclose(results[mode][1][pid], ref, rtol=1e-3, atol=1e-4 * max(1.0, np.abs(ref).max()),
                                        err_msg=f"mode {mode} {pid}")
+
+
+def test_hundred_step_loss_curve_on_tensor_core_shapes(golden_dir):
+    """100 optimiser steps of a decoder that takes every tensor-core kernel (3xTF32 GEMMs with
+    the LoRA tails, rank-16 factor kernels, attention with scores / dP held in TMEM), fed by
+    the shuffled feeder: the loss at every step within 0.5 % of the reference runtime's curve
+    (fixture made by tests/golden/make_tc_curve.py), in fused and in contract mode."""
+    import json
+    import os
+    import tccase
+    from see_ml_b200.engine import Dataset, UpdateEngine
+    lib = L.lib()
+    want = json.load(open(os.path.join(golden_dir, "tc_curve.json")))
+    model, spec, toks = tccase.build()
+    blob = tccase.plan(model, spec, lambda b, o: int(
+        lib.seeml_b200_plan_self_hash(np.frombuffer(b, np.uint8).ctypes.data, len(b), o)))
+    for mode in (1, 0):
+        e = UpdateEngine(0, mode, 0)
+        e.load_from_memory(blob)
+        ds = Dataset.from_tokens(toks)
+        ds.enable_shuffle(7)
+        res = e.train(ds, tccase.STEPS)
+        assert res.steps == want["steps"] == tccase.STEPS
+        np.testing.assert_allclose(res.loss_curve, want["curve"], rtol=5e-3, err_msg=f"mode {mode}")
+        assert res.loss_curve[-1] < 0.7 * res.loss_curve[0]          # it actually learned
+        assert abs(res.final_avg_loss - want["final_avg_loss"]) <= 5e-3 * want["final_avg_loss"]
+        e.close()
