@@ -302,6 +302,10 @@ def run_ours(args, cfg):
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     clocks = sampler.stop() if rank == 0 else None
     loss_a = tr.engine.loss_value()
+    # digest of the persistent segment (adapters + optimiser state) after warm-up + timed steps:
+    # equal across GPU counts for equal --steps/--warmup, since the gradient tree is fixed
+    import hashlib
+    params_digest = hashlib.sha256(tr.persistent().tobytes()).hexdigest()[:16]
     ms_step = ms_total / args.steps
     tokens = rows * K
     value = tokens / (ms_step * 1e-3)
@@ -377,7 +381,7 @@ def run_ours(args, cfg):
                 "data": "synthetic", "config": workload_config(args, cfg),
                 "mode": "fused" if args.fused else "contract",
                 "gemm_tflops_algorithmic": flops * K / (ms_step * 1e-3) / 1e12,
-                "loss": loss_a, "e2e": e2e, "gpu_launches": int(launches),
+                "loss": loss_a, "params_sha256_16": params_digest, "e2e": e2e, "gpu_launches": int(launches),
                 "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)
     tr.close()
