@@ -591,6 +591,240 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// ------------------------------------------------ CTA-pair GEMM (cta_group::2, 3xTF32 only)
+// Two CTAs of a cluster (consecutive 128-row tiles of M) share one 256 x 256 output tile: each
+// stages its own 128 rows of A and HALF of the B tile (128 of the 256 rows of B^T), and the
+// even CTA issues tcgen05.mma.cta_group::2 with M = 256 - the hardware reads A and the B halves
+// from both CTAs' shared memory and leaves 128 x 256 accumulators in each CTA's TMEM. Per SM
+// that is 8 KB of operand reads per MMA instead of 12 KB and half the B staging, which lifts
+// the shared-memory bound of the single-CTA kernel; the smaller stages also allow three.
+//
+// Protocol: loads complete on each CTA's own barrier; the worker warps of BOTH CTAs arrive on
+// the even CTA's "split" barrier once their tiles are split; the even CTA's MMA thread waits on
+// that, issues, and commits with a multicast arrive to both CTAs' "empty" (stage reusable) and
+// "accumulator full" barriers; collectors of both CTAs arrive on the even CTA's "accumulator
+// empty" barrier. TMEM is allocated / freed by warp 1 of both CTAs (cta_group::2 forms). A cluster
+// barrier after the barrier initialisation and one before exit keep remote arrivals and the
+// peer's operand reads inside the lifetime of both CTAs. Every mbarrier wait is bounded.
+constexpr int kPairStages = 3;
+struct PairSmem {
+  static constexpr int kA = BM * BK * 4, kBh = 128 * BK * 4;     // A tile, half B tile: 16 KiB each
+  static constexpr int kStage = 2 * kA + 2 * kBh;                // [A raw][A lo][B raw][B lo]
+  static constexpr int kTotal = kPairStages * kStage + 256 + 1024;
+};
+
+__global__ void __launch_bounds__(kThreadsV2, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                    const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapA2,
+                    const __grid_constant__ CUtensorMap mapB2, const __grid_constant__ CUtensorMap mapBlo,
+                    TcParams p) {
+  using S = PairSmem;
+  constexpr int STAGES = kPairStages, BN = 256;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + STAGES * S::kStage;
+  auto bar_full = [&](int s) { return bars + 8u * s; };
+  auto bar_split = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+  auto bar_acc_full = [&](int b) { return bars + 8u * (3 * STAGES + b); };
+  auto bar_acc_empty = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 4);
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (3 * STAGES + 4));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0: issues the MMAs; 1: its peer
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int nkb1 = (p.K + BK - 1) / BK;
+  const int nkb = nkb1 + (p.K2 + BK - 1) / BK;
+  const int nchunks = (nkb + kChunk - 1) / kChunk;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_split(s), 2 * kWorkers / 32); // one arrival per worker warp of both CTAs (used in the even CTA)
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), 2 * kWorkers / 32);  // one per collector warp of both CTAs (used in the even CTA)
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                               // the peer's barriers exist before anyone arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ---- TMA producer (each CTA loads its own tiles onto its own barrier) -------------------
+    if (lane == 0) {
+      int issued = 0;
+      bool ok = true;
+      const int nb = n0 + (int)rank * 128;          // this CTA's half of the B tile
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % STAGES, r = kb / STAGES;
+        if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 31);
+        if (!ok) break;
+        const uint32_t a_dst = base + s * S::kStage, b_dst = a_dst + 2 * S::kA;
+        const bool lo_too = p.b_lo && kb < nkb1;
+        mbar_expect_tx(bar_full(s), S::kA + S::kBh + (lo_too ? S::kBh : 0));
+        if (kb < nkb1) {
+          tma_load_2d(a_dst, &mapA, bar_full(s), kb * BK, m0);
+          tma_load_2d(b_dst, &mapB, bar_full(s), kb * BK, nb);
+          if (lo_too) tma_load_2d(b_dst + S::kBh, &mapBlo, bar_full(s), kb * BK, nb);
+        } else {
+          tma_load_2d(a_dst, &mapA2, bar_full(s), (kb - nkb1) * BK, m0);
+          tma_load_2d(b_dst, &mapB2, bar_full(s), (kb - nkb1) * BK, nb);
+        }
+        ++issued;
+      }
+      if (!ok) {
+        for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb)
+          mbar_wait(bar_full(kb % STAGES), (kb / STAGES) & 1, p.err, 35);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: the even CTA only --------------------------------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = idesc_tf32(256, BN);
+      bool ok = true;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES, r = kb / STAGES;
+        const int ci = kb / kChunk, buf = ci & 1;
+        if (kb % kChunk == 0 && ci >= 2) {
+          ok = mbar_wait(bar_acc_empty(buf), ((ci >> 1) - 1) & 1, p.err, 36);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        ok = mbar_wait(bar_split(s), r & 1, p.err, 32);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        const uint32_t a_raw = base + s * S::kStage, a_lo = a_raw + S::kA;
+        const uint32_t b_raw = a_raw + 2 * S::kA, b_lo = b_raw + S::kBh;
+#pragma unroll
+        for (int kk = 0; kk < BK / 8; ++kk) {
+          const uint64_t da = smem_desc_sw128(a_raw + kk * 32), db = smem_desc_sw128(b_raw + kk * 32);
+          mma_tf32_pair(tmem_d, da, db, idesc, ((kb % kChunk) | kk) != 0);
+          mma_tf32_pair(tmem_d, smem_desc_sw128(a_lo + kk * 32), db, idesc, 1);
+          mma_tf32_pair(tmem_d, da, smem_desc_sw128(b_lo + kk * 32), idesc, 1);
+        }
+        mma_commit_pair(bar_empty(s));
+        if (kb % kChunk == kChunk - 1 || kb == nkb - 1) mma_commit_pair(bar_acc_full(buf));
+      }
+    }
+  } else {
+    // ---- worker warps (both CTAs): split, collect finished chunks, epilogue -------------------
+    const int t = threadIdx.x - 64;
+    const int q = warp & 3, half = (warp - 2) >> 2, row0 = q * 32;
+    constexpr int NH = BN / 2, LD = 32;
+    float acc[NH];
+#pragma unroll
+    for (int j = 0; j < NH; ++j) acc[j] = 0.0f;
+    bool ok = true;
+    int collected = 0;
+    auto collect = [&](int ci) {
+      const int buf = ci & 1;
+      if (!mbar_wait(bar_acc_full(buf), (ci >> 1) & 1, p.err, 34)) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < NH / LD; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + buf * BN + half * NH + c * LD, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(bar_acc_empty(buf), 0);     // remote arrivals are slow: one per warp
+      return true;
+    };
+    auto split_range = [&](uint8_t* raw, int bytes) {
+      const float4* rp = reinterpret_cast<const float4*>(raw);
+      float4* lp = reinterpret_cast<float4*>(raw + bytes);
+#pragma unroll 4
+      for (int i = t; i < bytes / 16; i += kWorkers) {
+        const float4 v = rp[i];
+        lp[i] = make_float4(lo_part(v.x), lo_part(v.y), lo_part(v.z), lo_part(v.w));
+      }
+    };
+    for (int kb = 0; kb < nkb && ok; ++kb) {
+      const int s = kb % STAGES, r = kb / STAGES;
+      ok = mbar_wait(bar_full(s), r & 1, p.err, 33);
+      if (!ok) break;
+      uint8_t* stg = base_ptr + s * S::kStage;
+      split_range(stg, S::kA);
+      if (!(p.b_lo && kb < nkb1)) split_range(stg + 2 * S::kA, S::kBh);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(bar_split(s), 0);
+      if (kb % kChunk == 1 && kb > kChunk) {
+        ok = collect(collected);
+        ++collected;
+      }
+    }
+    for (; ok && collected < nchunks; ++collected) ok = collect(collected);
+    if (ok && m0 + row0 < p.M) {
+#pragma unroll
+      for (int c = 0; c < NH / LD; ++c) {
+        const int ncol = n0 + half * NH + c * LD;
+        if (ncol < p.N) {
+          const uint32_t box = (uint32_t)(((warp - 2) * (NH / LD) + c) * 4096);
+          uint8_t* stage_ptr = base_ptr + box;
+          uint32_t r[32];
+#pragma unroll
+          for (int j = 0; j < LD; ++j) r[j] = __float_as_uint(p.alpha * acc[c * LD + j]);
+          if (p.addend != nullptr && m0 + row0 + lane < p.M) {
+            const float* arow = p.addend + (size_t)(m0 + row0 + lane) * p.N + ncol;
+#pragma unroll
+            for (int j4 = 0; j4 < LD / 4; ++j4) {
+              if (ncol + 4 * j4 < p.N) {
+                const float4 d = *reinterpret_cast<const float4*>(arow + 4 * j4);
+                r[4 * j4 + 0] = __float_as_uint(d.x + __uint_as_float(r[4 * j4 + 0]));
+                r[4 * j4 + 1] = __float_as_uint(d.y + __uint_as_float(r[4 * j4 + 1]));
+                r[4 * j4 + 2] = __float_as_uint(d.z + __uint_as_float(r[4 * j4 + 2]));
+                r[4 * j4 + 3] = __float_as_uint(d.w + __uint_as_float(r[4 * j4 + 3]));
+              }
+            }
+          }
+          if (p.bias != nullptr || p.act != 0) {
+#pragma unroll
+            for (int j = 0; j < LD; ++j) {
+              float v = __uint_as_float(r[j]);
+              if (p.bias != nullptr && ncol + j < p.N) v = v + p.bias[ncol + j];
+              r[j] = __float_as_uint(epi_act(p.act, v));
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < LD / 4; ++j) {
+            uint4 v = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            *reinterpret_cast<uint4*>(stage_ptr + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&mapC, base + box, ncol, m0 + row0);
+            tma_store_commit();
+          }
+        }
+      }
+      if (lane == 0) tma_store_wait_all();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                               // nobody leaves while the peer may still touch this CTA
+  if (warp == 1) tmem_dealloc2(tmem_base, 512);
+}
+
 // ------------------------------------------ attention forward: scores + causal softmax -> P
 // One CTA owns 128 query rows of one (batch item, head): the scaled scores of those rows
 // against every key up to the diagonal, (i + 1) * 128 columns, accumulate in TMEM (all 512
@@ -1036,6 +1270,45 @@ int launch_tc(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   return 1;
 }
 
+// The CTA-pair kernel for wide tiles: M tiles must pair up (an even number of 128-row tiles).
+int launch_pair(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kTotal) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+    attr_done = true;
+  }
+  const CUtensorMap* ma = cached_map(st, g.A, g.M, g.K, BM);
+  const CUtensorMap* mb = cached_map(st, g.Bt, g.N, g.K, 128);
+  const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
+  const CUtensorMap* ma2 = g.K2 ? cached_map(st, g.A2, g.M, g.K2, BM) : ma;
+  const CUtensorMap* mb2 = g.K2 ? cached_map(st, g.B2t, g.N, g.K2, 128) : mb;
+  const float* blo = nullptr;
+  auto it = st.lo_copies.find(g.Bt);
+  if (it != st.lo_copies.end()) blo = it->second;
+  const CUtensorMap* mblo = blo ? cached_map(st, blo, g.N, g.K, 128) : mb;
+  if (!ma || !mb || !mc || !ma2 || !mb2 || !mblo) return -1;
+  TcParams p{(int)g.M, (int)g.N, (int)g.K, (int)g.K2, g.bias, g.addend, g.act, g.alpha == 0.0f ? 1.0f : g.alpha,
+             blo != nullptr, st.err_dev};
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)((g.N + 255) / 256), (unsigned)((g.M + BM - 1) / BM));
+  cfg.blockDim = dim3(kThreadsV2);
+  cfg.dynamicSmemBytes = PairSmem::kTotal;
+  cfg.stream = c->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 2; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, *ma, *mb, *mc, *ma2, *mb2, *mblo, p) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return 1;
+}
+
 TcState* state_of(seeml_b200_ctx* c, bool create) {
   auto it = states().find(c);
   if (it == states().end()) {
@@ -1066,7 +1339,10 @@ int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g) {
   const bool split = c->gemm_kind == SEEML_B200_GEMM_TF32X3;
   int r;
   static const bool half_blocks = [] { const char* e = std::getenv("SEEML_B200_GEMM_KB"); return e && std::atoi(e) == 16; }();
-  if (g.N >= 192 && split && half_blocks) r = launch_tc<256, true, 4, 16>(c, *st, g);
+  static const bool pairs = [] { const char* e = std::getenv("SEEML_B200_GEMM_PAIR"); return e && std::atoi(e) == 1; }();
+  const uint64_t m_tiles = (g.M + BM - 1) / BM;
+  if (g.N >= 192 && split && pairs && m_tiles % 2 == 0) r = launch_pair(c, *st, g);
+  else if (g.N >= 192 && split && half_blocks) r = launch_tc<256, true, 4, 16>(c, *st, g);
   else if (g.N >= 192) r = split ? launch_tc<256, true, 2>(c, *st, g) : launch_tc<256, false, 4>(c, *st, g);
   else r = split ? launch_tc<128, true, 3>(c, *st, g) : launch_tc<128, false, 6>(c, *st, g);
   if (r < 0) {   // tensor maps / attributes unavailable: leave the CUDA-core path in charge
