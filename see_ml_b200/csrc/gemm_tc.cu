@@ -23,6 +23,7 @@
 // backward GEMMs through frozen weights both take this K-major form.
 #include <cuda.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -606,9 +607,14 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
 // empty" barrier. TMEM is allocated / freed by warp 1 of both CTAs (cta_group::2 forms). A cluster
 // barrier after the barrier initialisation and one before exit keep remote arrivals and the
 // peer's operand reads inside the lifetime of both CTAs. Every mbarrier wait is bounded.
+// Three 32-wide stages. Measured alternatives that were slower: six 16-wide stages (the per-stage
+// signalling cost doubles), issuing the products that need no lo tile of A ahead of the split
+// on a separate "landed" barrier (an extra cross-CTA wait per stage), and L2 prefetch of the
+// tiles ahead of the ring (the load latency is not an L2-miss latency).
+constexpr int kPairKB = 32;
 constexpr int kPairStages = 3;
 struct PairSmem {
-  static constexpr int kA = BM * BK * 4, kBh = 128 * BK * 4;     // A tile, half B tile: 16 KiB each
+  static constexpr int kA = BM * kPairKB * 4, kBh = 128 * kPairKB * 4;   // A tile, half B tile: 8 KiB each
   static constexpr int kStage = 2 * kA + 2 * kBh;                // [A raw][A lo][B raw][B lo]
   static constexpr int kTotal = kPairStages * kStage + 256 + 1024;
 };
@@ -619,7 +625,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                     const __grid_constant__ CUtensorMap mapB2, const __grid_constant__ CUtensorMap mapBlo,
                     TcParams p) {
   using S = PairSmem;
-  constexpr int STAGES = kPairStages, BN = 256;
+  constexpr int STAGES = kPairStages, BN = 256, KB = kPairKB;
+  constexpr int kChunkBlocks = kChunk * (BK / KB);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -635,10 +642,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0: issues the MMAs; 1: its peer
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
-  const int nkb1 = (p.K + BK - 1) / BK;
-  const int nkb = nkb1 + (p.K2 + BK - 1) / BK;
-  const int nchunks = (nkb + kChunk - 1) / kChunk;
+  const int n0 = blockIdx.y * BN, m0 = blockIdx.x * BM;   // the pair = two consecutive M tiles (cluster along x)
+  const int nkb1 = (p.K + KB - 1) / KB;
+  const int nkb = nkb1 + (p.K2 + KB - 1) / KB;
+  const int nchunks = (nkb + kChunkBlocks - 1) / kChunkBlocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -676,12 +683,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         const bool lo_too = p.b_lo && kb < nkb1;
         mbar_expect_tx(bar_full(s), S::kA + S::kBh + (lo_too ? S::kBh : 0));
         if (kb < nkb1) {
-          tma_load_2d(a_dst, &mapA, bar_full(s), kb * BK, m0);
-          tma_load_2d(b_dst, &mapB, bar_full(s), kb * BK, nb);
-          if (lo_too) tma_load_2d(b_dst + S::kBh, &mapBlo, bar_full(s), kb * BK, nb);
+          tma_load_2d(a_dst, &mapA, bar_full(s), kb * KB, m0);
+          tma_load_2d(b_dst, &mapB, bar_full(s), kb * KB, nb);
+          if (lo_too) tma_load_2d(b_dst + S::kBh, &mapBlo, bar_full(s), kb * KB, nb);
         } else {
-          tma_load_2d(a_dst, &mapA2, bar_full(s), (kb - nkb1) * BK, m0);
-          tma_load_2d(b_dst, &mapB2, bar_full(s), (kb - nkb1) * BK, nb);
+          tma_load_2d(a_dst, &mapA2, bar_full(s), (kb - nkb1) * KB, m0);
+          tma_load_2d(b_dst, &mapB2, bar_full(s), (kb - nkb1) * KB, nb);
         }
         ++issued;
       }
@@ -697,8 +704,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       bool ok = true;
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % STAGES, r = kb / STAGES;
-        const int ci = kb / kChunk, buf = ci & 1;
-        if (kb % kChunk == 0 && ci >= 2) {
+        const int ci = kb / kChunkBlocks, buf = ci & 1;
+        if (kb % kChunkBlocks == 0 && ci >= 2) {
           ok = mbar_wait(bar_acc_empty(buf), ((ci >> 1) - 1) & 1, p.err, 36);
           if (!ok) break;
           tc_fence_after();
@@ -710,14 +717,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         const uint32_t a_raw = base + s * S::kStage, a_lo = a_raw + S::kA;
         const uint32_t b_raw = a_raw + 2 * S::kA, b_lo = b_raw + S::kBh;
 #pragma unroll
-        for (int kk = 0; kk < BK / 8; ++kk) {
-          const uint64_t da = smem_desc_sw128(a_raw + kk * 32), db = smem_desc_sw128(b_raw + kk * 32);
-          mma_tf32_pair(tmem_d, da, db, idesc, ((kb % kChunk) | kk) != 0);
-          mma_tf32_pair(tmem_d, smem_desc_sw128(a_lo + kk * 32), db, idesc, 1);
-          mma_tf32_pair(tmem_d, da, smem_desc_sw128(b_lo + kk * 32), idesc, 1);
+        for (int kk = 0; kk < KB / 8; ++kk) {
+          const uint64_t da = smem_desc_k<KB>(a_raw + kk * 32), db = smem_desc_k<KB>(b_raw + kk * 32);
+          mma_tf32_pair(tmem_d, da, db, idesc, ((kb % kChunkBlocks) | kk) != 0);
+          mma_tf32_pair(tmem_d, smem_desc_k<KB>(a_lo + kk * 32), db, idesc, 1);
+          mma_tf32_pair(tmem_d, da, smem_desc_k<KB>(b_lo + kk * 32), idesc, 1);
         }
         mma_commit_pair(bar_empty(s));
-        if (kb % kChunk == kChunk - 1 || kb == nkb - 1) mma_commit_pair(bar_acc_full(buf));
+        if (kb % kChunkBlocks == kChunkBlocks - 1 || kb == nkb - 1) mma_commit_pair(bar_acc_full(buf));
       }
     }
   } else {
@@ -766,7 +773,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(bar_split(s), 0);
-      if (kb % kChunk == 1 && kb > kChunk) {
+      if (kb % kChunkBlocks == 1 && kb > kChunkBlocks) {
         ok = collect(collected);
         ++collected;
       }
@@ -1280,29 +1287,31 @@ int launch_pair(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
     }
     attr_done = true;
   }
-  const CUtensorMap* ma = cached_map(st, g.A, g.M, g.K, BM);
-  const CUtensorMap* mb = cached_map(st, g.Bt, g.N, g.K, 128);
+  constexpr uint32_t kw = kPairKB == BK ? 0 : kPairKB;
+  const CUtensorMap* ma = cached_map(st, g.A, g.M, g.K, BM, kw);
+  const CUtensorMap* mb = cached_map(st, g.Bt, g.N, g.K, 128, kw);
   const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
-  const CUtensorMap* ma2 = g.K2 ? cached_map(st, g.A2, g.M, g.K2, BM) : ma;
-  const CUtensorMap* mb2 = g.K2 ? cached_map(st, g.B2t, g.N, g.K2, 128) : mb;
+  const CUtensorMap* ma2 = g.K2 ? cached_map(st, g.A2, g.M, g.K2, BM, kw) : ma;
+  const CUtensorMap* mb2 = g.K2 ? cached_map(st, g.B2t, g.N, g.K2, 128, kw) : mb;
   const float* blo = nullptr;
   auto it = st.lo_copies.find(g.Bt);
   if (it != st.lo_copies.end()) blo = it->second;
-  const CUtensorMap* mblo = blo ? cached_map(st, blo, g.N, g.K, 128) : mb;
+  const CUtensorMap* mblo = blo ? cached_map(st, blo, g.N, g.K, 128, kw) : mb;
   if (!ma || !mb || !mc || !ma2 || !mb2 || !mblo) return -1;
   TcParams p{(int)g.M, (int)g.N, (int)g.K, (int)g.K2, g.bias, g.addend, g.act, g.alpha == 0.0f ? 1.0f : g.alpha,
              blo != nullptr, st.err_dev};
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)((g.N + 255) / 256), (unsigned)((g.M + BM - 1) / BM));
+  cfg.gridDim = dim3((unsigned)((g.M + BM - 1) / BM), (unsigned)((g.N + 255) / 256));
   cfg.blockDim = dim3(kThreadsV2);
   cfg.dynamicSmemBytes = PairSmem::kTotal;
   cfg.stream = c->stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 2; attr[0].val.clusterDim.z = 1;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, *ma, *mb, *mc, *ma2, *mb2, *mblo, p) != cudaSuccess) {
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, *ma, *mb, *mc, *ma2, *mb2, *mblo, p);
+  if (le != cudaSuccess) {
     cudaGetLastError();
     return -1;
   }
@@ -1339,7 +1348,7 @@ int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g) {
   const bool split = c->gemm_kind == SEEML_B200_GEMM_TF32X3;
   int r;
   static const bool half_blocks = [] { const char* e = std::getenv("SEEML_B200_GEMM_KB"); return e && std::atoi(e) == 16; }();
-  static const bool pairs = [] { const char* e = std::getenv("SEEML_B200_GEMM_PAIR"); return e && std::atoi(e) == 1; }();
+  static const bool pairs = [] { const char* e = std::getenv("SEEML_B200_GEMM_PAIR"); return !e || std::atoi(e) != 0; }();
   const uint64_t m_tiles = (g.M + BM - 1) / BM;
   if (g.N >= 192 && split && pairs && m_tiles % 2 == 0) r = launch_pair(c, *st, g);
   else if (g.N >= 192 && split && half_blocks) r = launch_tc<256, true, 4, 16>(c, *st, g);
