@@ -642,7 +642,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0: issues the MMAs; 1: its peer
-  const int n0 = blockIdx.y * BN, m0 = blockIdx.x * BM;   // the pair = two consecutive M tiles (cluster along x)
+  // The cluster runs along x (two consecutive CTAs = one pair of M tiles). Clusters are handed out in
+  // launch order, so the tile is taken from the linear cluster index with the N tile fastest: the
+  // clusters in flight share their rows of A and walk the (small, L2-resident) weight.
+  const uint32_t lin = blockIdx.y * gridDim.x + blockIdx.x, n_tiles = gridDim.y;
+  const int n0 = (int)((lin >> 1) % n_tiles) * BN, m0 = (int)(2 * ((lin >> 1) / n_tiles) + (lin & 1)) * BM;
   const int nkb1 = (p.K + KB - 1) / KB;
   const int nkb = nkb1 + (p.K2 + KB - 1) / KB;
   const int nchunks = (nkb + kChunkBlocks - 1) / kChunkBlocks;
