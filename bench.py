@@ -89,7 +89,7 @@ def plan_work(plan_bytes):
             by_shape[(m, n, k)] = by_shape.get((m, n, k), 0) + fl
     top = None
     if by_shape:
-        shape = max(sorted(by_shape), key=lambda sh: by_shape[sh])
+        shape = max(sorted(by_shape), key=lambda sh: (by_shape[sh], sh[1]))   # ties: the wider output
         top = (2 * shape[0] * shape[1] * shape[2], shape)
     return total, top
 
