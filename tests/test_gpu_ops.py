@@ -7,6 +7,7 @@ import numpy as np
 import pytest
 
 import opcases
+from see_ml_b200 import formats as F
 from oracle import pyoracle as O
 
 pytestmark = pytest.mark.gpu
@@ -97,3 +98,63 @@ def test_kernels_are_run_to_run_bit_reproducible():
         _, a = _run_case(c, gemm=0)
         _, b = _run_case(c, gemm=0)
         np.testing.assert_array_equal(a, b, err_msg=c.name)
+
+
+@pytest.mark.parametrize("kn", [(1024, 1024), (1024, 2816), (2816, 1024), (4096, 4096)], ids=lambda s: f"K{s[0]}xN{s[1]}")
+def test_lora_matmul_sweep_forward_dgrad_wgrad(kn):
+    """The MatMul/LoRA sweep at its smallest M (2048 rows; entries ~N(0,1), r in {8, 16, 64}):
+    forward Y = X.W + (alpha/r).(X.A).B and the backward group (dX, dA, dB), written as the
+    instruction sequences the compiler emits, run as a fused program and instruction by
+    instruction, against an f64 reference. Tolerance rel 1e-3 / abs 1e-4 scaled by the output's
+    magnitude (sums of 1024-4096 unit-variance products are ~32-64 in size)."""
+    from see_ml_b200.engine import Context, MODE_CONTRACT, MODE_FUSED
+    from see_ml_b200.formats import Op
+    K, N = kn
+    M = 2048
+    rng = np.random.default_rng(K * 7 + N)
+    for r in (8, 16, 64):
+        alpha = 2.0 * r
+        X, W = opcases._rn(rng, M, K), opcases._rn(rng, K, N)
+        A, B = opcases._rn(rng, K, r), opcases._rn(rng, r, N)
+        G = opcases._rn(rng, M, N)
+        L = opcases.Layout()
+        x, a, b, g = L.put(X), L.put(A), L.put(B), L.put(G)
+        w = L.put(W, ro=True)
+        c, t, u, s, y = L.out(M * N), L.out(M * r), L.out(M * N), L.out(M * N), L.out(M * N)
+        ds, dt, dB, dx1, dA, dx2, dX = (L.out(M * N), L.out(M * r), L.out(r * N), L.out(M * K), L.out(K * r),
+                                       L.out(M * K), L.out(M * K))
+        arena, ro = L.done()
+        sc = F.f32_bits(alpha / r)
+        I = opcases._ins
+        prog = np.concatenate([
+            I(Op.GEMM_NN, [x, w, c], [M, N, K]), I(Op.GEMM_NN, [x, a, t], [M, r, K]),
+            I(Op.GEMM_NN, [t, b, u], [M, N, r]), I(Op.SCALE, [u, s, sc], [M * N]), I(Op.ADD, [c, s, y], [M * N]),
+            I(Op.SCALE, [g, ds, sc], [M * N]), I(Op.GEMM_NT, [ds, b, dt], [M, r, N]),
+            I(Op.GEMM_TN, [t, ds, dB], [r, N, M]), I(Op.GEMM_NT, [dt, a, dx1], [M, K, r]),
+            I(Op.GEMM_TN, [x, dt, dA], [K, r, M]), I(Op.GEMM_NT, [g, w, dx2], [M, K, N]),
+            I(Op.ADD, [dx1, dx2, dX], [M * K])])
+        X64, W64, A64, B64, G64 = (v.astype(np.float64) for v in (X, W, A, B, G))
+        T64 = X64 @ A64
+        ref = {"y": X64 @ W64 + (alpha / r) * T64 @ B64}
+        dS64 = (alpha / r) * G64
+        dT64 = dS64 @ B64.T
+        ref["dB"], ref["dA"] = T64.T @ dS64, X64.T @ dT64
+        ref["dX"] = dT64 @ A64.T + G64 @ W64.T
+        outs = {"y": (y, M * N), "dB": (dB, r * N), "dA": (dA, K * r), "dX": (dX, M * K)}
+        launches = {}
+        for mode in (MODE_FUSED, MODE_CONTRACT):
+            ctx = Context(arena.size, ro, gemm=0)
+            ctx.write(0, arena)
+            pid = ctx.build(prog, mode=mode)
+            ctx.run(pid, 0, len(prog))
+            launches[mode] = ctx.launches(pid)
+            for name, (off, count) in outs.items():
+                got = ctx.read(off, count * 4).view(np.float32).astype(np.float64)
+                want = ref[name].reshape(-1)
+                scale = max(1.0, float(np.abs(want).max()) / 8.0)
+                err = np.abs(got - want)
+                assert np.all(err <= 1e-4 * scale + 1e-3 * np.abs(want)), \
+                    f"K{K} N{N} r{r} mode {mode} {name}: max err {err.max():.3e} at |ref| max {np.abs(want).max():.3e}"
+            ctx.close()
+        if r >= 16:
+            assert launches[MODE_FUSED] < launches[MODE_CONTRACT], "the LoRA groups were not fused"
