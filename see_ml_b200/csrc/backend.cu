@@ -499,7 +499,7 @@ void seeml_b200_ctx_destroy(seeml_b200_ctx* c) {
   cudaStreamSynchronize(c->copy_stream);
   for (auto& p : c->programs)
     if (p) {
-      for (auto& g : p->graphs) cudaGraphExecDestroy(g.second);
+      for (auto& g : p->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
       for (auto& fs : p->steps) cudaFree(fs.bt);
     }
   gemm_tensor_core_release(c);
@@ -530,6 +530,13 @@ void* seeml_b200_ctx_stream(seeml_b200_ctx* c) { return c ? c->stream : nullptr;
 int seeml_b200_ctx_set_gemm(seeml_b200_ctx* c, uint32_t kind) {
   if (!c) return fail("UpdateEngine: null context");
   if (kind > SEEML_B200_GEMM_TF32) return fail("UpdateEngine: unknown GEMM kind");
+  if (c->gemm_kind != kind) {     // captured graphs hold the previous kind's kernels
+    for (auto& p : c->programs)
+      if (p) {
+        for (auto& g : p->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+        p->graphs.clear();
+      }
+  }
   c->gemm_kind = kind;
   return 0;
 }
@@ -574,21 +581,59 @@ int seeml_b200_program_run(seeml_b200_ctx* c, int id, uint64_t begin, uint64_t e
   CU(cudaSetDevice(c->device), "cudaSetDevice");
   if (c->timing) CU(cudaEventRecord(c->t0, c->stream), "event record");
   upload_scalars(c, scalars);
+  static const bool graphs_off = [] { const char* e = std::getenv("SEEML_B200_GRAPHS"); return e && std::atoi(e) == 0; }();
+  Program::RangeGraph* rg = nullptr;
+  if (c->use_graphs && !graphs_off && end - begin >= 8) rg = &p.graphs[std::make_pair(begin, end)];
+  if (rg && rg->exec) {
+    CU(cudaGraphLaunch(rg->exec, c->stream), "graph launch");
+    p.last_launches = rg->launches;
+    if (c->timing) {
+      CU(cudaEventRecord(c->t1, c->stream), "event record");
+      c->timed_valid = true;
+    }
+    return 0;
+  }
+  const bool capture = rg && !rg->disabled && rg->runs >= 1;
+  if (rg) ++rg->runs;
+  if (capture && cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    cudaGetLastError();
+    rg->disabled = true;
+    return seeml_b200_program_run(c, id, begin, end, scalars);
+  }
   Exec x{c};
   x.launches = 1;
-  for (uint64_t i = begin; i < end;) {
+  int failed = 0;
+  for (uint64_t i = begin; i < end && !failed;) {
     const int32_t si = p.step_at.empty() ? -1 : p.step_at[i];
     if (si >= 0 && i + p.steps[si].count <= end) {
       const int fr = run_fused(x, p, p.steps[si]);
-      if (fr < 0) return 1;
+      if (fr < 0) { failed = 1; break; }
       if (fr == 1) { i += p.steps[si].count; continue; }
-      for (uint32_t q = 0; q < p.steps[si].count; ++q)
-        if (int r = dispatch(x, p.instrs[i + q])) return r;
+      for (uint32_t q = 0; q < p.steps[si].count && !failed; ++q) failed = dispatch(x, p.instrs[i + q]);
       i += p.steps[si].count;
       continue;
     }
-    if (int r = dispatch(x, p.instrs[i])) return r;
+    failed = dispatch(x, p.instrs[i]);
     ++i;
+  }
+  if (capture) {
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(c->stream, &graph);
+    if (failed || ce != cudaSuccess || !graph ||
+        cudaGraphInstantiate(&rg->exec, graph, 0) != cudaSuccess) {
+      // something in this range cannot be captured: run it directly from now on
+      cudaGetLastError();
+      if (graph) cudaGraphDestroy(graph);
+      rg->exec = nullptr;
+      rg->disabled = true;
+      if (failed) return failed;
+      return seeml_b200_program_run(c, id, begin, end, scalars);
+    }
+    cudaGraphDestroy(graph);
+    rg->launches = x.launches;
+    CU(cudaGraphLaunch(rg->exec, c->stream), "graph launch");
+  } else if (failed) {
+    return failed;
   }
   p.last_launches = x.launches;
   if (c->timing) {

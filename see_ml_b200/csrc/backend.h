@@ -100,8 +100,17 @@ struct Program {
   uint32_t version = kSeeuVersion;
   uint32_t mode = SEEML_B200_MODE_CONTRACT;
   uint64_t last_launches = 0;
-  // captured graphs per executed range
-  std::map<std::pair<uint64_t, uint64_t>, cudaGraphExec_t> graphs;
+  // One CUDA graph per executed instruction range: the first run of a range executes directly
+  // (lazy allocations and attribute calls happen there), the second is captured, later runs
+  // replay the graph. The step scalars live in device memory and are written before each launch,
+  // so a graph stays valid from step to step.
+  struct RangeGraph {
+    int runs = 0;
+    bool disabled = false;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t launches = 0;
+  };
+  std::map<std::pair<uint64_t, uint64_t>, RangeGraph> graphs;
 };
 
 }  // namespace seeml_b200
@@ -124,7 +133,7 @@ struct seeml_b200_ctx {
   uint64_t rodata_bytes = 0;
   uint32_t gemm_kind = SEEML_B200_GEMM_TF32X3;
   bool timing = false, timed_valid = false;
-  bool use_graphs = false;
+  bool use_graphs = true;          // SEEML_B200_GRAPHS=0 turns graph replay off
   seeml_b200::DevScalars* scalars_dev = nullptr;
   double* loss_scratch = nullptr;
   uint64_t loss_scratch_doubles = 0;
