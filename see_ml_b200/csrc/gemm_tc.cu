@@ -346,6 +346,7 @@ struct BgParams {
   int H;
   int ax[2], ay[2], bx[2], by[2], cx[2], cy[2];
   int x3;                  // three products (f32-class accuracy) or one
+  int pair_m;              // 0, or the number of M tiles when each CTA takes tiles y and (tiles - 1 - y)
   int* err;
 };
 
@@ -402,18 +403,28 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
   auto bar_acc_full = [&](int b) { return bars + 8u * (3 * STAGES + b); };
   auto bar_acc_empty = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
-  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 4);
+  const uint32_t bar_epi = bars + 8u * (3 * STAGES + 4);       // first tile's store staging has been read
+  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 5);
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (3 * STAGES + 4));
+      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (3 * STAGES + 5));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int n0 = blockIdx.x * BN;
   const int bi = blockIdx.z / p.H, hd = blockIdx.z % p.H;
-  int kb_begin = 0, kb_end = p.nkb;
-  if (p.causal == 1 && n0 > m0 + BM - 1) kb_end = 0;
-  if (p.causal == 2) kb_end = min(kb_end, (m0 + BM) / BK);
-  if (p.causal == 3) kb_begin = min(kb_end, m0 / BK);
-  const int nk = kb_end - kb_begin;
+  // A CTA owns one M tile, or - for the causal reductions, whose length grows with the tile index -
+  // the tiles y and (tiles - 1 - y): equal work per CTA, and the second tile's loads run under the
+  // first tile's epilogue. The stage ring and the chunk counter run on across the two tiles.
+  const int ntile = p.pair_m ? 2 : 1;
+  auto tile_of = [&](int ti, int& m0, int& kb_begin, int& nk) {
+    const int mt = ti == 0 ? (int)blockIdx.y : p.pair_m - 1 - (int)blockIdx.y;
+    m0 = mt * BM;
+    kb_begin = 0;
+    int kb_end = p.nkb;
+    if (p.causal == 1 && n0 > m0 + BM - 1) kb_end = 0;
+    if (p.causal == 2) kb_end = min(kb_end, (m0 + BM) / BK);
+    if (p.causal == 3) kb_begin = min(kb_end, m0 / BK);
+    nk = kb_end - kb_begin;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -425,6 +436,7 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       mbar_init(bar_acc_full(b), 1);
       mbar_init(bar_acc_empty(b), 128);
     }
+    mbar_init(bar_epi, 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // 3xTF32 with the hi and lo tiles of B adjacent in shared memory: one MMA of width 2*BN
@@ -454,21 +466,29 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     if (lane == 0) {
       const int ax0 = bi * p.ax[0] + hd * p.ax[1], ay0 = bi * p.ay[0] + hd * p.ay[1];
       const int bx0 = bi * p.bx[0] + hd * p.bx[1], by0 = bi * p.by[0] + hd * p.by[1];
-      int issued = 0;
+      int it = 0, epi_stage = -1;       // epi_stage: the stage the first tile's epilogue stages its stores in
       bool ok = true;
-      for (int i = 0; i < nk && ok; ++i) {
-        const int s = i % STAGES, r = i / STAGES, k0 = (kb_begin + i) * BK;
-        if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 11);
-        if (!ok) break;
-        mbar_expect_tx(bar_full(s), S::kA + S::kB);
-        if (TA) tma_load_2d(base + a_raw(s), &mapA, bar_full(s), ax0 + m0, ay0 + k0);
-        else tma_load_2d(base + a_raw(s), &mapA, bar_full(s), ax0 + k0, ay0 + m0);
-        if (TB) tma_load_2d(base + b_raw(s), &mapB, bar_full(s), bx0 + n0, by0 + k0);
-        else tma_load_2d(base + b_raw(s), &mapB, bar_full(s), bx0 + k0, by0 + n0);
-        ++issued;
+      for (int ti = 0; ti < ntile && ok; ++ti) {
+        int m0, kb_begin, nk;
+        tile_of(ti, m0, kb_begin, nk);
+        for (int i = 0; i < nk && ok; ++i, ++it) {
+          const int s = it % STAGES, r = it / STAGES, k0 = (kb_begin + i) * BK;
+          if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 11);
+          if (ok && s == epi_stage) {
+            ok = mbar_wait(bar_epi, 0, p.err, 17);
+            epi_stage = -1;
+          }
+          if (!ok) break;
+          mbar_expect_tx(bar_full(s), S::kA + S::kB);
+          if (TA) tma_load_2d(base + a_raw(s), &mapA, bar_full(s), ax0 + m0, ay0 + k0);
+          else tma_load_2d(base + a_raw(s), &mapA, bar_full(s), ax0 + k0, ay0 + m0);
+          if (TB) tma_load_2d(base + b_raw(s), &mapB, bar_full(s), bx0 + n0, by0 + k0);
+          else tma_load_2d(base + b_raw(s), &mapB, bar_full(s), bx0 + k0, by0 + n0);
+        }
+        if (ti == 0 && ntile == 2 && it > 0) epi_stage = (it - 1) % STAGES;
       }
       if (!ok) {
-        for (int i = (issued > STAGES ? issued - STAGES : 0); i < issued; ++i)
+        for (int i = (it > STAGES ? it - STAGES : 0); i < it; ++i)
           mbar_wait(bar_full(i % STAGES), (i / STAGES) & 1, p.err, 15);
       }
     }
@@ -476,9 +496,13 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_tf32(BM, BN), idesc2 = idesc_tf32(BM, 2 * BN);
       bool ok = true;
-      for (int i = 0; i < nk; ++i) {
-        const int s = i % STAGES, r = i / STAGES;
-        const int ci = i / kChunk, buf = ci & 1;
+      int it = 0, ci = 0;               // k-blocks and accumulation chunks issued so far, over both tiles
+      for (int ti = 0; ti < ntile && ok; ++ti) {
+      int m0, kb_begin, nk;
+      tile_of(ti, m0, kb_begin, nk);
+      for (int i = 0; i < nk; ++i, ++it) {
+        const int s = it % STAGES, r = it / STAGES;
+        const int buf = ci & 1;
         if (i % kChunk == 0 && ci >= 2) {
           ok = mbar_wait(bar_acc_empty(buf), ((ci >> 1) - 1) & 1, p.err, 16);
           if (!ok) break;
@@ -499,7 +523,11 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           }
         }
         mma_commit(bar_empty(s));
-        if (i % kChunk == kChunk - 1 || i == nk - 1) mma_commit(bar_acc_full(buf));
+        if (i % kChunk == kChunk - 1 || i == nk - 1) {
+          mma_commit(bar_acc_full(buf));
+          ++ci;
+        }
+      }
       }
     }
   } else {
@@ -509,10 +537,7 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     // finished chunks are added into f32 registers while the next chunk is multiplied (the
     // tensor core's own accumulation truncates; see gemm_tc_kernel)
     float acc[BN];
-#pragma unroll
-    for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
-    const int nchunks = (nk + kChunk - 1) / kChunk;
-    int collected = 0;
+    int it = 0, cg = 0;                             // k-blocks split / chunks collected so far, over both tiles
     const bool collector = warp < 6;               // warps 2..5: one per TMEM lane quadrant
     auto collect = [&](int ci) {
       if (!collector) return true;
@@ -537,8 +562,16 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       mbar_arrive(bar_acc_empty(buf));
       return true;
     };
-    for (int i = 0; i < nk && ok; ++i) {
-      const int s = i % STAGES, r = i / STAGES;
+    for (int ti = 0; ti < ntile && ok; ++ti) {
+    int m0, kb_begin, nk;
+    tile_of(ti, m0, kb_begin, nk);
+    (void)kb_begin;
+#pragma unroll
+    for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
+    const int nchunks = (nk + kChunk - 1) / kChunk;
+    int collected = 0;
+    for (int i = 0; i < nk && ok; ++i, ++it) {
+      const int s = it % STAGES, r = it / STAGES;
       ok = mbar_wait(bar_full(s), r & 1, p.err, 13);
       if (!ok) break;
       if (TA) split_transposed<BM>(base_ptr + a_raw(s), base_ptr + a_hi(s), base_ptr + a_lo(s), t);
@@ -548,15 +581,19 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       fence_async_smem();
       mbar_arrive(bar_split(s));
       if (i % kChunk == 1 && i > kChunk) {
-        ok = collect(collected);
+        ok = collect(cg);
+        ++cg;
         ++collected;
       }
     }
-    for (; ok && collected < nchunks; ++collected) ok = collect(collected);
+    for (; ok && collected < nchunks; ++collected, ++cg) ok = collect(cg);
     if (ok && collector) {
-      // every product has retired, so the first stage's buffers serve as store staging
-      const uint32_t stage = base + q * 4096;
-      uint8_t* stage_ptr = base_ptr + q * 4096;
+      // every product of this tile has retired: the stage of its last k-block is the one the
+      // producer refills last, so it serves as store staging (the producer waits for bar_epi
+      // before it loads into that stage again)
+      const uint32_t soff = (uint32_t)((it > 0 ? (it - 1) % STAGES : 0) * S::kStage) + q * 4096;
+      const uint32_t stage = base + soff;
+      uint8_t* stage_ptr = base_ptr + soff;
       const int cx0 = bi * p.cx[0] + hd * p.cx[1], cy0 = bi * p.cy[0] + hd * p.cy[1];
       const int m = m0 + row0 + lane;
       for (int c = 0; c < BN / LD; ++c) {
@@ -584,8 +621,18 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           tma_store_commit();
         }
       }
-      if (lane == 0) tma_store_wait_all();
+      if (lane == 0) {
+        if (ti + 1 < ntile) {
+          tma_store_wait_read();
+          mbar_arrive(bar_epi);
+        } else {
+          tma_store_wait_all();
+        }
+      }
+      __syncwarp();
     }
+    }
+    if (collector && lane == 0) tma_store_wait_all();
   }
   tc_fence_before();
   __syncthreads();
@@ -1389,7 +1436,9 @@ int launch_bg(seeml_b200_ctx* c, TcState& st, const TcBatched& g) {
   }
   p.x3 = c->gemm_kind == SEEML_B200_GEMM_TF32X3;
   p.err = st.err_dev;
-  dim3 grid((unsigned)(g.N / BN), (unsigned)(g.M / BM), (unsigned)g.batch);
+  const int m_tiles = g.M / BM;
+  p.pair_m = ((g.causal == 2 || g.causal == 3) && m_tiles % 2 == 0) ? m_tiles : 0;
+  dim3 grid((unsigned)(g.N / BN), (unsigned)(p.pair_m ? m_tiles / 2 : m_tiles), (unsigned)g.batch);
   kern<<<grid, kThreadsTC, S::kTotal, c->stream>>>(*ma, *mb, *mc, p);
   return 1;
 }
