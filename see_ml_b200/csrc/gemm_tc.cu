@@ -23,6 +23,7 @@
 // backward GEMMs through frozen weights both take this K-major form.
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -48,6 +49,7 @@ struct TcParams {
   int act;               // 0 none 1 relu 2 gelu 3 silu
   float alpha;           // scales the product before addend / bias / activation
   int b_lo;              // the lo tiles of B (main pair) come from a precomputed copy through mapBlo
+  int n_tiles, total_tiles;   // pair kernel: 256-wide N tiles, and 256 x 256 tiles in all
   int* err;              // device error word
 };
 
@@ -683,17 +685,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
   auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
   auto bar_acc_full = [&](int b) { return bars + 8u * (3 * STAGES + b); };
   auto bar_acc_empty = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
-  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 4);
+  const uint32_t bar_epi = bars + 8u * (3 * STAGES + 4);     // this CTA's store staging of a tile has been read
+  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 5);
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (3 * STAGES + 4));
+      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (3 * STAGES + 5));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0: issues the MMAs; 1: its peer
-  // The cluster runs along x (two consecutive CTAs = one pair of M tiles). Clusters are handed out in
-  // launch order, so the tile is taken from the linear cluster index with the N tile fastest: the
-  // clusters in flight share their rows of A and walk the (small, L2-resident) weight.
-  const uint32_t lin = blockIdx.y * gridDim.x + blockIdx.x, n_tiles = gridDim.y;
-  const int n0 = (int)((lin >> 1) % n_tiles) * BN, m0 = (int)(2 * ((lin >> 1) / n_tiles) + (lin & 1)) * BM;
+  // Persistent clusters (one per SM pair, laid along x): cluster c takes tiles c, c + clusters, ...
+  // in an order with the N tile fastest, so the clusters in flight share their rows of A and walk
+  // the (small, L2-resident) weight. The stage ring, the accumulation-chunk counter and the
+  // barriers' phases run on across tiles: the next tile's loads are in flight, and its MMAs can
+  // start, while the workers store the finished tile from registers.
+  const int cid = (int)(blockIdx.x >> 1), ncl = (int)(gridDim.x >> 1);
+  auto tile_of = [&](int t, int& m0, int& n0) {
+    n0 = (t % p.n_tiles) * BN;
+    m0 = (2 * (t / p.n_tiles) + (int)rank) * BM;
+  };
   const int nkb1 = (p.K + KB - 1) / KB;
   const int nkb = nkb1 + (p.K2 + KB - 1) / KB;
   const int nchunks = (nkb + kChunkBlocks - 1) / kChunkBlocks;
@@ -708,6 +716,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       mbar_init(bar_acc_full(b), 1);
       mbar_init(bar_acc_empty(b), 2 * kWorkers / 32);  // one per collector warp of both CTAs (used in the even CTA)
     }
+    mbar_init(bar_epi, kWorkers / 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -723,28 +732,41 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
   if (warp == 0) {
     // ---- TMA producer (each CTA loads its own tiles onto its own barrier) -------------------
     if (lane == 0) {
-      int issued = 0;
+      int it = 0, ti = 0, pend = -1, epi_stage = -1;   // pend: tile whose store staging may still be in use
       bool ok = true;
-      const int nb = n0 + (int)rank * 128;          // this CTA's half of the B tile
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        const int s = kb % STAGES, r = kb / STAGES;
-        if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 31);
-        if (!ok) break;
-        const uint32_t a_dst = base + s * S::kStage, b_dst = a_dst + 2 * S::kA;
-        const bool lo_too = p.b_lo && kb < nkb1;
-        mbar_expect_tx(bar_full(s), S::kA + S::kBh + (lo_too ? S::kBh : 0));
-        if (kb < nkb1) {
-          tma_load_2d(a_dst, &mapA, bar_full(s), kb * KB, m0);
-          tma_load_2d(b_dst, &mapB, bar_full(s), kb * KB, nb);
-          if (lo_too) tma_load_2d(b_dst + S::kBh, &mapBlo, bar_full(s), kb * KB, nb);
-        } else {
-          tma_load_2d(a_dst, &mapA2, bar_full(s), (kb - nkb1) * KB, m0);
-          tma_load_2d(b_dst, &mapB2, bar_full(s), (kb - nkb1) * KB, nb);
+      for (int tl = cid; tl < p.total_tiles && ok; tl += ncl, ++ti) {
+        int m0, n0;
+        tile_of(tl, m0, n0);
+        const int nb = n0 + (int)rank * 128;        // this CTA's half of the B tile
+        for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+          const int s = it % STAGES, r = it / STAGES;
+          if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 31);
+          if (ok && pend >= 0 && s == epi_stage) {  // the previous tile's epilogue staged its stores here
+            ok = mbar_wait(bar_epi, pend & 1, p.err, 38);
+            pend = -1;
+          }
+          if (!ok) break;
+          const uint32_t a_dst = base + s * S::kStage, b_dst = a_dst + 2 * S::kA;
+          const bool lo_too = p.b_lo && kb < nkb1;
+          mbar_expect_tx(bar_full(s), S::kA + S::kBh + (lo_too ? S::kBh : 0));
+          if (kb < nkb1) {
+            tma_load_2d(a_dst, &mapA, bar_full(s), kb * KB, m0);
+            tma_load_2d(b_dst, &mapB, bar_full(s), kb * KB, nb);
+            if (lo_too) tma_load_2d(b_dst + S::kBh, &mapBlo, bar_full(s), kb * KB, nb);
+          } else {
+            tma_load_2d(a_dst, &mapA2, bar_full(s), (kb - nkb1) * KB, m0);
+            tma_load_2d(b_dst, &mapB2, bar_full(s), (kb - nkb1) * KB, nb);
+          }
         }
-        ++issued;
+        if (ok && pend >= 0) {                      // short tiles: take the phase anyway, in order
+          ok = mbar_wait(bar_epi, pend & 1, p.err, 38);
+          pend = -1;
+        }
+        pend = ti;
+        epi_stage = (it - 1) % STAGES;
       }
       if (!ok) {
-        for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb)
+        for (int kb = (it > STAGES ? it - STAGES : 0); kb < it; ++kb)
           mbar_wait(bar_full(kb % STAGES), (kb / STAGES) & 1, p.err, 35);
       }
     }
@@ -753,9 +775,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = idesc_tf32(256, BN);
       bool ok = true;
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % STAGES, r = kb / STAGES;
-        const int ci = kb / kChunkBlocks, buf = ci & 1;
+      int it = 0, ci = 0;
+      for (int tl = cid; tl < p.total_tiles && ok; tl += ncl)
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = it % STAGES, r = it / STAGES;
+        const int buf = ci & 1;
         if (kb % kChunkBlocks == 0 && ci >= 2) {
           ok = mbar_wait(bar_acc_empty(buf), ((ci >> 1) - 1) & 1, p.err, 36);
           if (!ok) break;
@@ -775,7 +799,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
           mma_tf32_pair(tmem_d, da, smem_desc_k<KB>(b_lo + kk * 32), idesc, 1);
         }
         mma_commit_pair(bar_empty(s));
-        if (kb % kChunkBlocks == kChunkBlocks - 1 || kb == nkb - 1) mma_commit_pair(bar_acc_full(buf));
+        if (kb % kChunkBlocks == kChunkBlocks - 1 || kb == nkb - 1) {
+          mma_commit_pair(bar_acc_full(buf));
+          ++ci;
+        }
       }
     }
   } else {
@@ -784,10 +811,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const int q = warp & 3, half = (warp - 2) >> 2, row0 = q * 32;
     constexpr int NH = BN / 2, LD = 32;
     float acc[NH];
-#pragma unroll
-    for (int j = 0; j < NH; ++j) acc[j] = 0.0f;
     bool ok = true;
-    int collected = 0;
+    int it = 0, cg = 0;
     auto collect = [&](int ci) {
       const int buf = ci & 1;
       if (!mbar_wait(bar_acc_full(buf), (ci >> 1) & 1, p.err, 34)) return false;
@@ -814,8 +839,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         lp[i] = make_float4(lo_part(v.x), lo_part(v.y), lo_part(v.z), lo_part(v.w));
       }
     };
-    for (int kb = 0; kb < nkb && ok; ++kb) {
-      const int s = kb % STAGES, r = kb / STAGES;
+    for (int tl = cid; tl < p.total_tiles && ok; tl += ncl) {
+    int m0, n0;
+    tile_of(tl, m0, n0);
+#pragma unroll
+    for (int j = 0; j < NH; ++j) acc[j] = 0.0f;
+    int collected = 0;
+    for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+      const int s = it % STAGES, r = it / STAGES;
       ok = mbar_wait(bar_full(s), r & 1, p.err, 33);
       if (!ok) break;
       uint8_t* stg = base_ptr + s * S::kStage;
@@ -825,18 +856,28 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(bar_split(s), 0);
       if (kb % kChunkBlocks == 1 && kb > kChunkBlocks) {
-        ok = collect(collected);
+        ok = collect(cg);
+        ++cg;
         ++collected;
       }
     }
-    for (; ok && collected < nchunks; ++collected) ok = collect(collected);
-    if (ok && m0 + row0 < p.M) {
+    for (; ok && collected < nchunks; ++collected, ++cg) ok = collect(cg);
+    if (!ok) break;
+    // every product of the tile has retired; the stage of its last k-block is the one the producer
+    // refills last, so it holds the store staging (one 32x32 box per warp, reused chunk by chunk)
+    const uint32_t box = (uint32_t)(((it - 1) % STAGES) * S::kStage + (warp - 2) * 4096);
+    if (m0 + row0 < p.M) {
+      bool stored = false;
 #pragma unroll
       for (int c = 0; c < NH / LD; ++c) {
         const int ncol = n0 + half * NH + c * LD;
         if (ncol < p.N) {
-          const uint32_t box = (uint32_t)(((warp - 2) * (NH / LD) + c) * 4096);
           uint8_t* stage_ptr = base_ptr + box;
+          if (stored) {
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+          }
+          stored = true;
           uint32_t r[32];
 #pragma unroll
           for (int j = 0; j < LD; ++j) r[j] = __float_as_uint(p.alpha * acc[c * LD + j]);
@@ -874,8 +915,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
           }
         }
       }
-      if (lane == 0) tma_store_wait_all();
     }
+    if (lane == 0) {
+      tma_store_wait_read();                          // the staging may be overwritten by the next tile's loads
+      mbar_arrive(bar_epi);
+    }
+    __syncwarp();
+    }
+    if (lane == 0) tma_store_wait_all();
   }
   tc_fence_before();
   __syncthreads();
@@ -1260,6 +1307,7 @@ struct TcState {
   bool attrs_set = false;
   bool usable = true;
   float* rank_scratch = nullptr;
+  int pair_clusters = 0;          // resident clusters of the pair kernel on this device (0 = not queried yet)
   std::map<const float*, float*> lo_copies;   // frozen B operand -> its precomputed lo part (x - tf32(x))
   std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> maps;
 };
@@ -1322,7 +1370,7 @@ int launch_tc(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   const CUtensorMap* mblo = blo ? cached_map(st, blo, g.N, g.K, BN, kw) : mb;
   if (!ma || !mb || !mc || !ma2 || !mb2 || !mblo) return -1;
   TcParams p{(int)g.M, (int)g.N, (int)g.K, (int)g.K2, g.bias, g.addend, g.act, g.alpha == 0.0f ? 1.0f : g.alpha,
-             blo != nullptr, st.err_dev};
+             blo != nullptr, 0, 0, st.err_dev};
   dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((g.M + BM - 1) / BM));
   kern<<<grid, kThreadsV2, S::kTotal, c->stream>>>(*ma, *mb, *mc, *ma2, *mb2, *mblo, p);
   return 1;
@@ -1350,9 +1398,11 @@ int launch_pair(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   const CUtensorMap* mblo = blo ? cached_map(st, blo, g.N, g.K, 128, kw) : mb;
   if (!ma || !mb || !mc || !ma2 || !mb2 || !mblo) return -1;
   TcParams p{(int)g.M, (int)g.N, (int)g.K, (int)g.K2, g.bias, g.addend, g.act, g.alpha == 0.0f ? 1.0f : g.alpha,
-             blo != nullptr, st.err_dev};
+             blo != nullptr, 0, 0, st.err_dev};
+  p.n_tiles = (int)((g.N + 255) / 256);
+  p.total_tiles = p.n_tiles * (int)(((g.M + BM - 1) / BM) / 2);
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)((g.M + BM - 1) / BM), (unsigned)((g.N + 255) / 256));
+  cfg.gridDim = dim3(2u * (unsigned)std::min(p.total_tiles, st.pair_clusters > 0 ? st.pair_clusters : 74));
   cfg.blockDim = dim3(kThreadsV2);
   cfg.dynamicSmemBytes = PairSmem::kTotal;
   cfg.stream = c->stream;
