@@ -1402,7 +1402,6 @@ int launch_pair(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   p.n_tiles = (int)((g.N + 255) / 256);
   p.total_tiles = p.n_tiles * (int)(((g.M + BM - 1) / BM) / 2);
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(2u * (unsigned)std::min(p.total_tiles, st.pair_clusters > 0 ? st.pair_clusters : 74));
   cfg.blockDim = dim3(kThreadsV2);
   cfg.dynamicSmemBytes = PairSmem::kTotal;
   cfg.stream = c->stream;
@@ -1411,6 +1410,18 @@ int launch_pair(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (st.pair_clusters == 0) {       // one persistent cluster per SM pair the device can keep resident
+    cfg.gridDim = dim3(2u * 1024u);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 74;
+    }
+    if (const char* e = std::getenv("SEEML_B200_PAIR_PERSIST"))
+      if (std::atoi(e) == 0) n = 1 << 20;      // one tile per cluster (measurement aid)
+    st.pair_clusters = n;
+  }
+  cfg.gridDim = dim3(2u * (unsigned)std::min(p.total_tiles, st.pair_clusters));
   const cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, *ma, *mb, *mc, *ma2, *mb2, *mblo, p);
   if (le != cudaSuccess) {
     cudaGetLastError();
