@@ -501,6 +501,7 @@ void seeml_b200_ctx_destroy(seeml_b200_ctx* c) {
     if (p) {
       for (auto& g : p->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
       for (auto& fs : p->steps) cudaFree(fs.bt);
+      cudaFree(p->side);
     }
   gemm_tensor_core_release(c);
   for (auto& kv : c->wt) cudaFree(kv.second);

@@ -91,6 +91,7 @@ struct FusedStep {
   float* bt = nullptr;                          // side buffer: alpha * B_lora^T, [N, r]
   bool da_last = false;                         // dA after the dgrad GEMM (slot reuse, see backend_fuse.inc)
   bool via_temp = false;                        // result lands in a dead slot first, then moves
+  bool via_side = false;                        // result lands in the program's side buffer first, then moves
 };
 
 struct Program {
@@ -100,6 +101,7 @@ struct Program {
   uint32_t version = kSeeuVersion;
   uint32_t mode = SEEML_B200_MODE_CONTRACT;
   uint64_t last_launches = 0;
+  float* side = nullptr;                        // fused groups whose output slot aliases a live input stage here
   // One CUDA graph per executed instruction range: the first run of a range executes directly
   // (lazy allocations and attribute calls happen there), the second is captured, later runs
   // replay the graph. The step scalars live in device memory and are written before each launch,
