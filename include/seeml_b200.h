@@ -164,7 +164,10 @@ int seeml_b200_last_run_ms(seeml_b200_ctx* ctx, float* ms);
  * (cudaGetSymbolAddress) with that device current: make that first call outside any
  * stream capture. Every call uses the same array: two calls that may overlap on the
  * GPU (different streams, no ordering between them) race on it. Nothing in the array
- * has to start at zero; each call overwrites what it reads. */
+ * has to start at zero; each call overwrites what it reads.
+ * The operands must live on the CURRENT device (the call checks `logits` and refuses
+ * otherwise) and device ordinals 0..63 are supported. Every label must lie in
+ * [0, classes): a label outside that range is not dereferenced, it turns the loss into NaN. */
 int seeml_b200_xent_fwd_noalloc(const float* logits, const int32_t* labels, float* loss, float* probs,
                                 uint64_t rows, uint64_t classes, void* stream);
 

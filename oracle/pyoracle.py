@@ -25,8 +25,16 @@ def build_port():
     subprocess.run(["make", "-C", _HERE, "port"], check=True, capture_output=True)
 
 
-def build_ref(ref_root="/root/reference"):
-    if os.path.isdir(ref_root):
+def reference_root():
+    """Where a read-only checkout of the reference lies: $SEEML_REFERENCE_ROOT, else a
+    directory named ``reference`` beside this repository; None when there is none."""
+    root = os.environ.get("SEEML_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return root if os.path.isdir(os.path.join(root, "runtime", "engine")) else None
+
+
+def build_ref(ref_root=None):
+    ref_root = ref_root or reference_root()
+    if ref_root:
         subprocess.run(["make", "-C", _HERE, "-j8", "ref", f"REF={ref_root}"], check=True,
                        capture_output=True)
 

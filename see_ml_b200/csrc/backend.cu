@@ -94,7 +94,22 @@ int ensure_rope(seeml_b200_ctx* c, uint64_t S, uint64_t dh, float base) {
   return 0;
 }
 
+// Captured range graphs hold the addresses of the context's scratch buffers: whenever one of
+// those buffers is replaced, every graph of the context is dropped (its range is captured again
+// on a later run).
+void drop_graphs(seeml_b200_ctx* c) {
+  for (auto& p : c->programs)
+    if (p) {
+      for (auto& g : p->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+      p->graphs.clear();
+    }
+}
+
 int ensure_scratch(seeml_b200_ctx* c, uint64_t loss_doubles, uint64_t ws_floats) {
+  if (loss_doubles > c->loss_scratch_doubles || ws_floats > c->gemm_ws_floats) {
+    cudaStreamSynchronize(c->stream);     // nothing in flight may still use the old buffers
+    drop_graphs(c);
+  }
   if (loss_doubles > c->loss_scratch_doubles) {
     if (c->loss_scratch) cudaFree(c->loss_scratch);
     c->loss_scratch = nullptr;
@@ -266,7 +281,7 @@ int dispatch(Exec& x, const Instr& ins) {
     case kReduceRows: n = k::reduce_rows(x.R(in[0]), x.W(in[1]), o[0], o[1], st); break;
     case kFill: n = k::fill(x.W(in[0]), bits_f32(in[1]), o[0], st); break;
     case kCopy: n = k::copy(x.R(in[0]), x.W(in[1]), o[0], st); break;
-    case kEmbedFwd: n = k::embed(x.I(in[0]), x.R(in[1]), x.W(in[2]), o[0], lo32(o[1]), st); break;
+    case kEmbedFwd: n = k::embed(x.I(in[0]), x.R(in[1]), x.W(in[2]), o[0], lo32(o[1]), hi32(o[1]), st); break;
     case kLayerNormFwd:
       n = k::layernorm_fwd(x.R(in[0]), x.R(in[1]), x.R(in[2]), x.W(in[3]), x.W(o[1]), x.W(o[2]),
                            hi32(o[0]), lo32(o[0]), st);
@@ -531,13 +546,7 @@ void* seeml_b200_ctx_stream(seeml_b200_ctx* c) { return c ? c->stream : nullptr;
 int seeml_b200_ctx_set_gemm(seeml_b200_ctx* c, uint32_t kind) {
   if (!c) return fail("UpdateEngine: null context");
   if (kind > SEEML_B200_GEMM_TF32) return fail("UpdateEngine: unknown GEMM kind");
-  if (c->gemm_kind != kind) {     // captured graphs hold the previous kind's kernels
-    for (auto& p : c->programs)
-      if (p) {
-        for (auto& g : p->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
-        p->graphs.clear();
-      }
-  }
+  if (c->gemm_kind != kind) drop_graphs(c);     // captured graphs hold the previous kind's kernels
   c->gemm_kind = kind;
   return 0;
 }

@@ -24,6 +24,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <set>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -1310,6 +1311,7 @@ struct TcState {
   int pair_clusters = 0;          // resident clusters of the pair kernel on this device (0 = not queried yet)
   std::map<const float*, float*> lo_copies;   // frozen B operand -> its precomputed lo part (x - tf32(x))
   std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> maps;
+  std::set<const void*> smem_attr_done;   // kernels whose dynamic shared-memory limit was raised on this context's device
 };
 std::map<seeml_b200_ctx*, TcState>& states() {
   static std::map<seeml_b200_ctx*, TcState> s;
@@ -1331,6 +1333,20 @@ const CUtensorMap* cached_map(TcState& st, const void* ptr, uint64_t rows, uint6
   return &st.maps.emplace(key, m).first->second;
 }
 
+// cudaFuncSetAttribute applies to the current device only, so the "already raised" note is kept
+// per context (a process may hold contexts on several GPUs).
+template <class K>
+bool ensure_smem_attr(TcState& st, K kern, int bytes) {
+  const void* fn = reinterpret_cast<const void*>(kern);
+  if (st.smem_attr_done.count(fn)) return true;
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  st.smem_attr_done.insert(fn);
+  return true;
+}
+
 }  // namespace
 
 bool gemm_tc_shape_ok(const seeml_b200_ctx* c, uint64_t M, uint64_t N, uint64_t K) {
@@ -1348,14 +1364,7 @@ template <int BN, bool SPLIT, int STAGES, int KB = BK>
 int launch_tc(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   using S = Smem<BN, SPLIT, STAGES, KB>;
   auto kern = gemm_tc_kernel<BN, SPLIT, STAGES, KB>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) {
-      cudaGetLastError();
-      return -1;
-    }
-    attr_done = true;
-  }
+  if (!ensure_smem_attr(st, kern, S::kTotal)) return -1;
   constexpr uint32_t kw = KB == BK ? 0 : KB;
   const CUtensorMap* ma = cached_map(st, g.A, g.M, g.K, BM, kw);
   const CUtensorMap* mb = cached_map(st, g.Bt, g.N, g.K, BN, kw);
@@ -1373,19 +1382,13 @@ int launch_tc(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
              blo != nullptr, 0, 0, st.err_dev};
   dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((g.M + BM - 1) / BM));
   kern<<<grid, kThreadsV2, S::kTotal, c->stream>>>(*ma, *mb, *mc, *ma2, *mb2, *mblo, p);
+  if (cudaGetLastError() != cudaSuccess) return -1;     // a refused launch leaves the CUDA-core path in charge
   return 1;
 }
 
 // The CTA-pair kernel for wide tiles: M tiles must pair up (an even number of 128-row tiles).
 int launch_pair(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kTotal) != cudaSuccess) {
-      cudaGetLastError();
-      return -1;
-    }
-    attr_done = true;
-  }
+  if (!ensure_smem_attr(st, gemm_tc_pair_kernel, PairSmem::kTotal)) return -1;
   constexpr uint32_t kw = kPairKB == BK ? 0 : kPairKB;
   const CUtensorMap* ma = cached_map(st, g.A, g.M, g.K, BM, kw);
   const CUtensorMap* mb = cached_map(st, g.Bt, g.N, g.K, 128, kw);
@@ -1478,14 +1481,7 @@ template <int BN, bool TA, bool TB, int STAGES>
 int launch_bg(seeml_b200_ctx* c, TcState& st, const TcBatched& g) {
   using S = BgSmem<BN, TA, TB, STAGES>;
   auto kern = bgemm_tc_kernel<BN, TA, TB, STAGES>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) {
-      cudaGetLastError();
-      return -1;
-    }
-    attr_done = true;
-  }
+  if (!ensure_smem_attr(st, kern, S::kTotal)) return -1;
   const CUtensorMap* ma = TA ? cached_map(st, g.A, g.a_rows, g.a_cols, BK, BM, true) : cached_map(st, g.A, g.a_rows, g.a_cols, BM);
   const CUtensorMap* mb = TB ? cached_map(st, g.B, g.b_rows, g.b_cols, BK, BN, true) : cached_map(st, g.B, g.b_rows, g.b_cols, BN);
   const CUtensorMap* mc = cached_map(st, g.C, g.c_rows, g.c_cols, 32);
@@ -1501,6 +1497,7 @@ int launch_bg(seeml_b200_ctx* c, TcState& st, const TcBatched& g) {
   p.pair_m = ((g.causal == 2 || g.causal == 3) && m_tiles % 2 == 0) ? m_tiles : 0;
   dim3 grid((unsigned)(g.N / BN), (unsigned)(p.pair_m ? m_tiles / 2 : m_tiles), (unsigned)g.batch);
   kern<<<grid, kThreadsTC, S::kTotal, c->stream>>>(*ma, *mb, *mc, p);
+  if (cudaGetLastError() != cudaSuccess) return -1;
   return 1;
 }
 }  // namespace
@@ -1630,15 +1627,10 @@ static int attn_rows_launch(seeml_b200_ctx* c, int mode, const float* A, const f
   TcState* st = state_of(c, false);
   if (!st || !st->usable || !st->err_dev) return 0;
   constexpr int kSmem = 12 * BM * BK * 4 + 4 * 128 * 12 + 256 + 1024;
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(attn_scores_softmax_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(attn_scores_softmax_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
-      cudaGetLastError();
-      st->usable = false;
-      return 0;
-    }
-    attr_done = true;
+  if (!ensure_smem_attr(*st, attn_scores_softmax_kernel<0>, kSmem) ||
+      !ensure_smem_attr(*st, attn_scores_softmax_kernel<1>, kSmem)) {
+    st->usable = false;
+    return 0;
   }
   const CUtensorMap* mq = cached_map(*st, A, B * S, H * dh, BM);
   const CUtensorMap* mk = cached_map(*st, Bm, B * S, H * dh, BM);
@@ -1652,6 +1644,10 @@ static int attn_rows_launch(seeml_b200_ctx* c, int mode, const float* A, const f
   dim3 grid((unsigned)(S / BM), (unsigned)(B * H));
   if (mode == 0) attn_scores_softmax_kernel<0><<<grid, kAfThreads, kSmem, c->stream>>>(*mq, *mk, *mp, p);
   else attn_scores_softmax_kernel<1><<<grid, kAfThreads, kSmem, c->stream>>>(*mq, *mk, *mp, p);
+  if (cudaGetLastError() != cudaSuccess) {
+    st->usable = false;
+    return 0;
+  }
   return 1;
 }
 int attn_scores_softmax_tc(seeml_b200_ctx* c, const float* Q, const float* K, float* P, uint64_t B, uint64_t S,

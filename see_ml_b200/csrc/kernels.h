@@ -28,7 +28,8 @@ int act_fwd(int act, const float* x, float* o, size_t n, cudaStream_t st);   // 
 int act_bwd(int act, const float* dy, const float* x, float* dx, size_t n, cudaStream_t st);
 int fill(float* d, float v, size_t n, cudaStream_t st);
 int copy(const float* s, float* d, size_t n, cudaStream_t st);
-int embed(const int32_t* tok, const float* table, float* o, size_t rows, size_t dim, cudaStream_t st);
+int embed(const int32_t* tok, const float* table, float* o, size_t rows, size_t dim, size_t vocab,
+          cudaStream_t st);
 int reduce_rows(const float* dy, float* db, size_t rows, size_t cols, cudaStream_t st);
 // bias + activation over finished GEMM rows (gemm.cc:145-169)
 int bias_act(float* c, const float* bias, size_t rows, size_t cols, int act, cudaStream_t st);

@@ -139,12 +139,17 @@ __global__ void __launch_bounds__(kThreads) bias_act_kernel(const float* __restr
 __global__ void __launch_bounds__(kThreads) embed_kernel(const int32_t* __restrict__ tok,
                                                          const float* __restrict__ table,
                                                          float* __restrict__ o, size_t rows,
-                                                         size_t dim, int vec) {
+                                                         size_t dim, size_t vocab, int vec) {
   const int lane = threadIdx.x & 31;
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
   for (size_t r = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
-    const float* src = table + (size_t)tok[r] * dim;
+    const uint32_t id = (uint32_t)tok[r];
     float* dst = o + r * dim;
+    if (id >= vocab) {      // an id outside the table (the engine proves this cannot happen): zeros, no wild read
+      for (size_t c = lane; c < dim; c += 32) dst[c] = 0.0f;
+      continue;
+    }
+    const float* src = table + (size_t)id * dim;
     if (vec) {
       for (size_t c = lane; c < (dim >> 2); c += 32)
         reinterpret_cast<float4*>(dst)[c] = reinterpret_cast<const float4*>(src)[c];
@@ -472,7 +477,8 @@ __global__ void __launch_bounds__(kThreads) xent_rows_kernel(
       if (TPR != 32) __syncthreads();
       else __syncwarp();
       if (lane == 0) {
-        const float pl = p[(size_t)labels[n]];
+        const uint32_t lab = (uint32_t)labels[n];      // a label outside [0, C) poisons the loss, it is not read
+        const float pl = lab < C ? p[lab] : __int_as_float(0x7fc00000);
         const double safe = isnan(pl) ? (double)pl : (double)fmaxf(pl, 1e-12f);
         terms[n] = -log(safe);
       }
@@ -773,10 +779,11 @@ int bias_act(float* c, const float* bias, size_t rows, size_t cols, int act, cud
   bias_act_kernel<<<grid_for(n / 4 + 1, kThreads), kThreads, 0, st>>>(c, bias, c, rows, cols, act);
   return 1;
 }
-int embed(const int32_t* tok, const float* table, float* o, size_t rows, size_t dim, cudaStream_t st) {
+int embed(const int32_t* tok, const float* table, float* o, size_t rows, size_t dim, size_t vocab,
+          cudaStream_t st) {
   if (rows == 0) return 0;
   const int vec = (dim % 4 == 0) && aligned16(table) && aligned16(o);
-  embed_kernel<<<grid_for(rows, kThreads / 32, 16), kThreads, 0, st>>>(tok, table, o, rows, dim, vec);
+  embed_kernel<<<grid_for(rows, kThreads / 32, 16), kThreads, 0, st>>>(tok, table, o, rows, dim, vocab, vec);
   return 1;
 }
 int reduce_rows(const float* dy, float* db, size_t rows, size_t cols, cudaStream_t st) {
