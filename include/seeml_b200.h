@@ -65,10 +65,13 @@ typedef struct seeml_b200_scalars {
  * into single kernels; ranges that no later instruction reads may be skipped. */
 #define SEEML_B200_MODE_CONTRACT 0u
 #define SEEML_B200_MODE_FUSED 1u
-/* GEMM arithmetic: 3xTF32 split (f32-class accuracy), single-pass TF32/BF16
- * inputs with f32 accumulation, or plain f32 FMA on the CUDA cores. */
+/* GEMM arithmetic. TF32X3: three tf32 products per step (hi.hi + lo.hi + hi.lo), f32-class
+ * accuracy. F16X2: the same three-product scheme on a two-term fp16 split of power-of-two-scaled
+ * operands, f32 accumulation (the same 22 significant bits at twice the tensor-core rate; taken
+ * by the wide frozen-weight GEMMs, every other shape runs TF32X3). TF32: one tf32 product
+ * (10-bit operands). FP32_SIMT: plain f32 FMA on the CUDA cores. */
 #define SEEML_B200_GEMM_TF32X3 0u
-#define SEEML_B200_GEMM_BF16 1u
+#define SEEML_B200_GEMM_F16X2 1u
 #define SEEML_B200_GEMM_FP32_SIMT 2u
 #define SEEML_B200_GEMM_TF32 3u
 
@@ -207,6 +210,10 @@ void seeml_b200_dataset_fill_batch(seeml_b200_dataset* d, uint64_t batch, void* 
 int seeml_b200_dataset_skip_served(seeml_b200_dataset* d, uint64_t rows);
 int seeml_b200_dataset_validate_labels(const seeml_b200_dataset* d, uint64_t num_classes);
 int seeml_b200_dataset_save(const seeml_b200_dataset* d, const char* path);
+uint64_t seeml_b200_dataset_label_bytes_per_sample(const seeml_b200_dataset* d);
+/* Dataset::SaveServingPos / RestoreServingPos — runtime/feeder/dataset.h:93-106. */
+void seeml_b200_dataset_save_pos(const seeml_b200_dataset* d, uint64_t* cursor, uint64_t* epoch);
+void seeml_b200_dataset_restore_pos(seeml_b200_dataset* d, uint64_t cursor, uint64_t epoch);
 
 /* --------------------------------------------------------------------- engine --
  * class UpdateEngine — runtime/engine/update_engine.h:119-190. */
@@ -277,6 +284,8 @@ int seeml_b200_engine_enable_step_timing(seeml_b200_engine* e, int on);
 int seeml_b200_engine_step_timings(const seeml_b200_engine* e, uint64_t* steps,
                                    double* fwd_seconds, double* bwd_seconds,
                                    double* opt_seconds);
+/* ResetStepTimings (update_engine.h:190). */
+int seeml_b200_engine_reset_step_timings(seeml_b200_engine* e);
 
 #ifdef __cplusplus
 }

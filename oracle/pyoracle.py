@@ -120,6 +120,7 @@ def ref():
         lib.ref_engine_save_checkpoint.argtypes = [vp, C.c_char_p, C.c_char_p, u64]
         lib.ref_engine_load_checkpoint.argtypes = [vp, C.c_char_p, C.c_char_p, u64]
         lib.ref_engine_step_timings.argtypes = [vp, vp, vp, vp, vp]
+        lib.ref_emit_native_package.argtypes = [vp, u64, C.c_char_p, C.c_char_p, C.c_char_p, u64]
         _ref = lib
     return _ref
 
@@ -307,3 +308,15 @@ def ref_compile(smf_path, out_path, batch, lora_rank=8, lora_alpha=16.0, lora_se
         raise RuntimeError(f"reference compile failed ({rc}): {err.value.decode()}")
     with open(out_path, "rb") as f:
         return f.read()
+
+
+def ref_emit_native_package(plan: bytes, out_dir: str, repo_root: str | None = None):
+    """Runs the reference compiler's packaging step on `plan`: the generated driver
+    (update_main.cc) and the embedded-plan translation unit land in `out_dir`. Returns the
+    emitter's error text ('' when the whole package, vendored runtime included, was written;
+    the vendoring needs a reference checkout, the two generated files do not)."""
+    buf = np.frombuffer(plan, np.uint8)
+    err = C.create_string_buffer(1024)
+    rc = ref().ref_emit_native_package(buf.ctypes.data, buf.size, out_dir.encode(),
+                                       (repo_root or "/nonexistent-reference-root").encode(), err, 1024)
+    return err.value.decode() if rc else ""

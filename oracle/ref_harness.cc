@@ -19,6 +19,7 @@
 #include <string>
 #include <vector>
 
+#include "compiler/backend/trainer/native_emitter.h"
 #include "compiler/driver/update_compiler.h"
 #include "compiler/frontend/ingressor/model_reader.h"
 #include "runtime/engine/update_engine.h"
@@ -467,6 +468,22 @@ void ref_engine_step_timings(void* e, uint64_t* steps, double* fwd, double* bwd,
   *fwd = t.fwd_seconds;
   *bwd = t.bwd_seconds;
   *opt = t.opt_seconds;
+}
+
+// The reference compiler's native packaging step (native_emitter.cc:420-...): writes
+// update_plan.seeu, update_plan_embedded.cc and the generated driver update_main.cc into
+// out_dir, then vendors the runtime sources from repo_root. Returns 0 when the whole
+// package was written; otherwise 1 with the emitter's message (the plan, embedded TU and
+// driver are written before the vendoring step, so they exist even when repo_root does not).
+int ref_emit_native_package(const uint8_t* plan, uint64_t size, const char* out_dir,
+                            const char* repo_root, char* err, uint64_t cap) {
+  std::vector<uint8_t> bytes(plan, plan + size);
+  auto r = up::EmitNativePackage(bytes, out_dir, repo_root ? repo_root : "");
+  if (!r) {
+    SetErr(err, cap, r.error());
+    return 1;
+  }
+  return 0;
 }
 
 }  // extern "C"

@@ -94,6 +94,9 @@ SIGNATURES = {
     "seeml_b200_dataset_skip_served": (INT, [vp, u64]),
     "seeml_b200_dataset_validate_labels": (INT, [vp, u64]),
     "seeml_b200_dataset_save": (INT, [vp, cp]),
+    "seeml_b200_dataset_label_bytes_per_sample": (u64, [vp]),
+    "seeml_b200_dataset_save_pos": (None, [vp, C.POINTER(u64), C.POINTER(u64)]),
+    "seeml_b200_dataset_restore_pos": (None, [vp, u64, u64]),
     "seeml_b200_engine_create": (vp, [INT, u32, u32]),
     "seeml_b200_engine_destroy": (None, [vp]),
     "seeml_b200_engine_load_memory": (INT, [vp, vp, u64]),
@@ -118,6 +121,7 @@ SIGNATURES = {
     "seeml_b200_engine_run_train_range": (INT, [vp, u64, u64]),
     "seeml_b200_engine_last_launches": (u64, [vp]),
     "seeml_b200_engine_enable_step_timing": (INT, [vp, INT]),
+    "seeml_b200_engine_reset_step_timings": (INT, [vp]),
     "seeml_b200_engine_step_timings": (INT, [vp, C.POINTER(u64), C.POINTER(C.c_double),
                                              C.POINTER(C.c_double), C.POINTER(C.c_double)]),
 }

@@ -349,4 +349,18 @@ int seeml_b200_dataset_save(const seeml_b200_dataset* d, const char* path) {
   return err.empty() ? 0 : fail(err);
 }
 
+/* Dataset::label_bytes_per_sample, SaveServingPos / RestoreServingPos (dataset.h:57, 93-106). */
+uint64_t seeml_b200_dataset_label_bytes_per_sample(const seeml_b200_dataset* d) {
+  return d ? d->label_bytes_per_sample() : 0;
+}
+void seeml_b200_dataset_save_pos(const seeml_b200_dataset* d, uint64_t* cursor, uint64_t* epoch) {
+  if (!d) return;
+  const seeml_b200_dataset::Pos p = d->save_pos();
+  if (cursor) *cursor = p.cursor;
+  if (epoch) *epoch = p.epoch;
+}
+void seeml_b200_dataset_restore_pos(seeml_b200_dataset* d, uint64_t cursor, uint64_t epoch) {
+  if (d) d->restore_pos({cursor, epoch});
+}
+
 }  // extern "C"

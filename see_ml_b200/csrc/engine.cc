@@ -522,6 +522,13 @@ int seeml_b200_engine_step_timings(const seeml_b200_engine* e, uint64_t* steps, 
   return 0;
 }
 
+int seeml_b200_engine_reset_step_timings(seeml_b200_engine* e) {
+  if (!e) return fail("UpdateEngine: null engine");
+  e->t_steps = 0;
+  e->t_fwd = e->t_bwd = e->t_opt = 0;
+  return 0;
+}
+
 int seeml_b200_engine_evaluate(seeml_b200_engine* e, seeml_b200_dataset* data, float* loss,
                                float* accuracy, int32_t* has_accuracy) {
   if (!e || !data) return fail("UpdateEngine: null argument");

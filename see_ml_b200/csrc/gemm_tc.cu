@@ -22,8 +22,10 @@
 // transposed [N,K] copy (made once, when the program is built) so forward and
 // backward GEMMs through frozen weights both take this K-major form.
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cmath>
 #include <set>
 #include <cstdio>
 #include <cstdlib>
@@ -36,6 +38,13 @@ namespace seeml_b200 {
 namespace {
 
 using namespace tc;
+
+// f32-class accuracy requested (a split product): the kernels other than the CTA-pair GEMM run
+// the three-product tf32 split in both of these modes.
+inline bool kind_x3(const seeml_b200_ctx* c) {
+  return c->gemm_kind == SEEML_B200_GEMM_TF32X3 || c->gemm_kind == SEEML_B200_GEMM_F16X2;
+}
+inline bool kind_tc(const seeml_b200_ctx* c) { return c->gemm_kind != SEEML_B200_GEMM_FP32_SIMT; }
 
 constexpr int BM = 128;
 constexpr int BK = 32;                 // f32 elements = one 128-byte swizzle row
@@ -931,6 +940,376 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
   if (warp == 1) tmem_dealloc2(tmem_base, 512);
 }
 
+
+// ----------------------------------------- CTA-pair GEMM, two-term fp16 split (F16X2)
+// The same 256 x 256 cluster tile, stage ring, chunked accumulation and epilogue as
+// gemm_tc_pair_kernel, with a different arithmetic: every f32 operand x is scaled by a power of
+// two s (chosen per tensor so that max|x| * s lies in [2^13, 2^14)) and cut into two fp16 terms,
+// hi = fp16(x s) and lo = fp16(x s - hi). a.b ~ (hi.hi + lo.hi + hi.lo) / (sa sb): the same 22
+// significant bits as the three-product tf32 split (the dropped lo.lo term is 2^-22 relative), but
+// kind::f16 multiplies at twice the tf32 rate and its tiles are half as wide in shared memory.
+// The power-of-two scale keeps fp16's narrow exponent range out of the result: after scaling, an
+// element is held to max(2^-22 |x s|, 2^-25), i.e. to 2^-39 of the tensor's largest magnitude at
+// worst. The scale is undone (exactly) when a finished chunk is added into the f32 registers, so
+// the main product and the low-rank tail - which have different scales - ride the same
+// accumulators as separate chunks.
+// A frozen B operand comes pre-split (fp16 hi / lo copies made when the program is built, loaded
+// by TMA with the 64-byte swizzle); every other operand is loaded as f32 and converted by the
+// worker warps. max|x| of the run-time operands is measured by absmax4_kernel just before.
+constexpr int kF16Raw = BM * 32 * 4;       // a 128 x 32 f32 tile
+constexpr int kF16Half = BM * 32 * 2;      // the same tile in fp16: 64-byte rows
+struct PairF16Smem {
+  static constexpr int kARaw = 0, kAHi = kF16Raw, kALo = kAHi + kF16Half, kBHi = kALo + kF16Half,
+                       kBLo = kBHi + kF16Half, kBRaw = kBLo + kF16Half;
+  static constexpr int kStage = kBRaw + kF16Raw;                   // 64 KiB
+  static constexpr int kTotal = kPairStages * kStage + 256 + 1024;
+};
+struct F16Params {
+  int M, N, K, K2;
+  const float* bias;
+  const float* addend;
+  int act;
+  float alpha;
+  int b_pre;                // the main pair's B tiles come pre-split through mapBhi / mapBlo
+  int eb_pre;               // scale exponent of those copies: they hold the split of w * 2^eb_pre
+  const uint32_t* absmax;   // device: bit patterns of max|x| over A, B, A2, B2 (B unused when b_pre)
+  int n_tiles, total_tiles;
+  int* err;
+};
+
+// Scale exponent e for a tensor whose largest magnitude has these bits: max * 2^e in [2^13, 2^14).
+// Zero, subnormal and non-finite maxima get no scaling.
+__host__ __device__ __forceinline__ int f16_scale_exp(uint32_t bits) {
+  const int ex = (int)((bits >> 23) & 0xFFu);
+  if (ex == 0 || ex == 0xFF) return 0;
+  const int e = 13 - (ex - 127);
+  return e < -120 ? -120 : (e > 120 ? 120 : e);
+}
+__device__ __forceinline__ float pow2i(int e) { return __int_as_float((e + 127) << 23); }
+
+// 128 rows x 32 f32 in the 128-byte swizzled layout of a TMA load -> the hi and lo fp16 tiles,
+// 64-byte rows in the 64-byte swizzled K-major layout the MMA reads.
+__device__ __forceinline__ void split_f16_tile(const uint8_t* raw, uint8_t* hi, uint8_t* lo, float sc, int t) {
+#pragma unroll
+  for (int i = t; i < kF16Raw / 16; i += kWorkers) {
+    const int row = i >> 3, c = (i & 7) ^ (row & 7);          // logical 16-byte chunk: k = 4c .. 4c+3
+    const float4 v = reinterpret_cast<const float4*>(raw)[i];
+    const float x0 = v.x * sc, x1 = v.y * sc, x2 = v.z * sc, x3 = v.w * sc;
+    const __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1), h2 = __float2half_rn(x2), h3 = __float2half_rn(x3);
+    const __half l0 = __float2half_rn(x0 - __half2float(h0)), l1 = __float2half_rn(x1 - __half2float(h1));
+    const __half l2 = __float2half_rn(x2 - __half2float(h2)), l3 = __float2half_rn(x3 - __half2float(h3));
+    const int off = row * 64 + ((((c >> 1) ^ (row >> 1)) & 3) << 4) + ((c & 1) << 3);
+    uint2 hv, lv;
+    hv.x = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+    hv.y = (uint32_t)__half_as_ushort(h2) | ((uint32_t)__half_as_ushort(h3) << 16);
+    lv.x = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+    lv.y = (uint32_t)__half_as_ushort(l2) | ((uint32_t)__half_as_ushort(l3) << 16);
+    *reinterpret_cast<uint2*>(hi + off) = hv;
+    *reinterpret_cast<uint2*>(lo + off) = lv;
+  }
+}
+
+__global__ void __launch_bounds__(kThreadsV2, 1)
+gemm_tc_pair_f16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                        const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapA2,
+                        const __grid_constant__ CUtensorMap mapB2, const __grid_constant__ CUtensorMap mapBhi,
+                        const __grid_constant__ CUtensorMap mapBlo, F16Params p) {
+  using S = PairF16Smem;
+  constexpr int STAGES = kPairStages, BN = 256, KB = 32;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + STAGES * S::kStage;
+  auto bar_full = [&](int s) { return bars + 8u * s; };
+  auto bar_split = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+  auto bar_acc_full = [&](int b) { return bars + 8u * (3 * STAGES + b); };
+  auto bar_acc_empty = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
+  const uint32_t bar_epi = bars + 8u * (3 * STAGES + 4);
+  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 5);
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (3 * STAGES + 5));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cid = (int)(blockIdx.x >> 1), ncl = (int)(gridDim.x >> 1);
+  auto tile_of = [&](int t, int& m0, int& n0) {
+    n0 = (t % p.n_tiles) * BN;
+    m0 = (2 * (t / p.n_tiles) + (int)rank) * BM;
+  };
+  // k-blocks of the main pair, then of the low-rank pair; accumulation chunks of up to kChunk
+  // blocks never straddle the two (their scales differ)
+  const int nkb1 = (p.K + KB - 1) / KB;
+  const int nkb = nkb1 + (p.K2 + KB - 1) / KB;
+  const int nmain = (nkb1 + kChunk - 1) / kChunk;
+  const int nchunks = nmain + (nkb - nkb1 + kChunk - 1) / kChunk;
+  auto chunk_pos = [&](int kb, int& c, int& j, bool& last) {
+    if (kb < nkb1) { c = kb / kChunk; j = kb % kChunk; last = j == kChunk - 1 || kb == nkb1 - 1; }
+    else { const int q = kb - nkb1; c = nmain + q / kChunk; j = q % kChunk; last = j == kChunk - 1 || kb == nkb - 1; }
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_split(s), 2 * kWorkers / 32);
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), 2 * kWorkers / 32);
+    }
+    mbar_init(bar_epi, kWorkers / 32);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ---- TMA producer ---------------------------------------------------------------------
+    if (lane == 0) {
+      int it = 0, ti = 0, pend = -1, epi_stage = -1;
+      bool ok = true;
+      for (int tl = cid; tl < p.total_tiles && ok; tl += ncl, ++ti) {
+        int m0, n0;
+        tile_of(tl, m0, n0);
+        const int nb = n0 + (int)rank * 128;
+        for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+          const int s = it % STAGES, r = it / STAGES;
+          if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 41);
+          if (ok && pend >= 0 && s == epi_stage) {
+            ok = mbar_wait(bar_epi, pend & 1, p.err, 48);
+            pend = -1;
+          }
+          if (!ok) break;
+          const uint32_t stg = base + s * S::kStage;
+          mbar_expect_tx(bar_full(s), 2 * kF16Raw);          // A raw + (B hi + B lo | B raw): 32 KiB either way
+          if (kb < nkb1) {
+            tma_load_2d(stg + S::kARaw, &mapA, bar_full(s), kb * KB, m0);
+            if (p.b_pre) {
+              tma_load_2d(stg + S::kBHi, &mapBhi, bar_full(s), kb * KB, nb);
+              tma_load_2d(stg + S::kBLo, &mapBlo, bar_full(s), kb * KB, nb);
+            } else {
+              tma_load_2d(stg + S::kBRaw, &mapB, bar_full(s), kb * KB, nb);
+            }
+          } else {
+            tma_load_2d(stg + S::kARaw, &mapA2, bar_full(s), (kb - nkb1) * KB, m0);
+            tma_load_2d(stg + S::kBRaw, &mapB2, bar_full(s), (kb - nkb1) * KB, nb);
+          }
+        }
+        if (ok && pend >= 0) {
+          ok = mbar_wait(bar_epi, pend & 1, p.err, 48);
+          pend = -1;
+        }
+        pend = ti;
+        epi_stage = (it - 1) % STAGES;
+      }
+      if (!ok) {
+        for (int kb = (it > STAGES ? it - STAGES : 0); kb < it; ++kb)
+          mbar_wait(bar_full(kb % STAGES), (kb / STAGES) & 1, p.err, 45);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: the even CTA only --------------------------------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = idesc_f16(256, BN);
+      bool ok = true;
+      int it = 0, ci = 0;
+      for (int tl = cid; tl < p.total_tiles && ok; tl += ncl)
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = it % STAGES, r = it / STAGES;
+        const int buf = ci & 1;
+        int c, j;
+        bool last;
+        chunk_pos(kb, c, j, last);
+        if (j == 0 && ci >= 2) {
+          ok = mbar_wait(bar_acc_empty(buf), ((ci >> 1) - 1) & 1, p.err, 46);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        ok = mbar_wait(bar_split(s), r & 1, p.err, 42);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        const uint32_t stg = base + s * S::kStage;
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {       // 16 fp16 of K (32 bytes) per instruction
+          const uint64_t da = smem_desc_sw64(stg + S::kAHi + kk * 32), dal = smem_desc_sw64(stg + S::kALo + kk * 32);
+          const uint64_t db = smem_desc_sw64(stg + S::kBHi + kk * 32), dbl = smem_desc_sw64(stg + S::kBLo + kk * 32);
+          mma_f16_pair(tmem_d, da, db, idesc, (j | kk) != 0);
+          mma_f16_pair(tmem_d, dal, db, idesc, 1);
+          mma_f16_pair(tmem_d, da, dbl, idesc, 1);
+        }
+        mma_commit_pair(bar_empty(s));
+        if (last) {
+          mma_commit_pair(bar_acc_full(buf));
+          ++ci;
+        }
+      }
+    }
+  } else {
+    // ---- worker warps (both CTAs): convert, collect finished chunks, epilogue -----------------
+    const int t = threadIdx.x - 64;
+    const int q = warp & 3, half = (warp - 2) >> 2, row0 = q * 32;
+    constexpr int NH = BN / 2, LD = 32;
+    const int ea = f16_scale_exp(p.absmax[0]), eb = p.b_pre ? p.eb_pre : f16_scale_exp(p.absmax[1]);
+    const int ea2 = f16_scale_exp(p.absmax[2]), eb2 = f16_scale_exp(p.absmax[3]);
+    const float sa = pow2i(ea), sb = pow2i(eb), sa2 = pow2i(ea2), sb2 = pow2i(eb2);
+    const float cs_main = pow2i(-ea) * pow2i(-eb), cs_tail = pow2i(-ea2) * pow2i(-eb2);
+    float acc[NH];
+    bool ok = true;
+    int it = 0, cg = 0;
+    auto collect = [&](int ci, float cs) {
+      const int buf = ci & 1;
+      if (!mbar_wait(bar_acc_full(buf), (ci >> 1) & 1, p.err, 44)) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < NH / LD; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + buf * BN + half * NH + c * LD, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]) * cs;   // cs is a power of two: exact
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(bar_acc_empty(buf), 0);
+      return true;
+    };
+    for (int tl = cid; tl < p.total_tiles && ok; tl += ncl) {
+    int m0, n0;
+    tile_of(tl, m0, n0);
+#pragma unroll
+    for (int j = 0; j < NH; ++j) acc[j] = 0.0f;
+    int collected = 0;
+    auto collect_to = [&](int upto) {          // collect this tile's chunks [collected, upto)
+      for (; ok && collected < upto; ++collected, ++cg) ok = collect(cg, collected < nmain ? cs_main : cs_tail);
+    };
+    for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+      const int s = it % STAGES, r = it / STAGES;
+      int c, j;
+      bool last;
+      chunk_pos(kb, c, j, last);
+      // the issuer cannot start chunk c before chunk c-2 has been collected, and this warp cannot
+      // get block kb before the issuer has retired block kb - STAGES
+      if (j == 0 && c >= 2) collect_to(c - 1);
+      if (!ok) break;
+      ok = mbar_wait(bar_full(s), r & 1, p.err, 43);
+      if (!ok) break;
+      uint8_t* stg = base_ptr + s * S::kStage;
+      const bool main_blk = kb < nkb1;
+      split_f16_tile(stg + S::kARaw, stg + S::kAHi, stg + S::kALo, main_blk ? sa : sa2, t);
+      if (!(p.b_pre && main_blk)) split_f16_tile(stg + S::kBRaw, stg + S::kBHi, stg + S::kBLo, main_blk ? sb : sb2, t);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(bar_split(s), 0);
+      if (j == 1) collect_to(c);              // the previous chunk, while the tensor core works on this one
+    }
+    collect_to(nchunks);
+    if (!ok) break;
+    const uint32_t box = (uint32_t)(((it - 1) % STAGES) * S::kStage + (warp - 2) * 4096);
+    if (m0 + row0 < p.M) {
+      bool stored = false;
+#pragma unroll
+      for (int c = 0; c < NH / LD; ++c) {
+        const int ncol = n0 + half * NH + c * LD;
+        if (ncol < p.N) {
+          uint8_t* stage_ptr = base_ptr + box;
+          if (stored) {
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+          }
+          stored = true;
+          uint32_t r[32];
+#pragma unroll
+          for (int j = 0; j < LD; ++j) r[j] = __float_as_uint(p.alpha * acc[c * LD + j]);
+          if (p.addend != nullptr && m0 + row0 + lane < p.M) {
+            const float* arow = p.addend + (size_t)(m0 + row0 + lane) * p.N + ncol;
+#pragma unroll
+            for (int j4 = 0; j4 < LD / 4; ++j4) {
+              if (ncol + 4 * j4 < p.N) {
+                const float4 d = *reinterpret_cast<const float4*>(arow + 4 * j4);
+                r[4 * j4 + 0] = __float_as_uint(d.x + __uint_as_float(r[4 * j4 + 0]));
+                r[4 * j4 + 1] = __float_as_uint(d.y + __uint_as_float(r[4 * j4 + 1]));
+                r[4 * j4 + 2] = __float_as_uint(d.z + __uint_as_float(r[4 * j4 + 2]));
+                r[4 * j4 + 3] = __float_as_uint(d.w + __uint_as_float(r[4 * j4 + 3]));
+              }
+            }
+          }
+          if (p.bias != nullptr || p.act != 0) {
+#pragma unroll
+            for (int j = 0; j < LD; ++j) {
+              float v = __uint_as_float(r[j]);
+              if (p.bias != nullptr && ncol + j < p.N) v = v + p.bias[ncol + j];
+              r[j] = __float_as_uint(epi_act(p.act, v));
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < LD / 4; ++j) {
+            uint4 v = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            *reinterpret_cast<uint4*>(stage_ptr + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&mapC, base + box, ncol, m0 + row0);
+            tma_store_commit();
+          }
+        }
+      }
+    }
+    if (lane == 0) {
+      tma_store_wait_read();
+      mbar_arrive(bar_epi);
+    }
+    __syncwarp();
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) tmem_dealloc2(tmem_base, 512);
+}
+
+// max|x| (as f32 bit patterns, which order like the magnitudes; a NaN sorts above every finite
+// value) of up to four tensors in one launch: blockIdx.y selects the tensor. The slots must be
+// zero beforehand. The maximum does not depend on the order of the atomic updates.
+struct AbsmaxArgs { const float* ptr[4]; unsigned long long n[4]; };
+__global__ void __launch_bounds__(256) absmax4_kernel(AbsmaxArgs a, uint32_t* __restrict__ slots) {
+  const float* x = a.ptr[blockIdx.y];
+  const size_t n = a.n[blockIdx.y];
+  if (x == nullptr || n == 0) return;
+  uint32_t m = 0;
+  const size_t n4 = n >> 2;
+  const uint4* x4 = reinterpret_cast<const uint4*>(x);
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 v = x4[i];
+    m = max(max(m, v.x & 0x7FFFFFFFu), max(max(v.y & 0x7FFFFFFFu, v.z & 0x7FFFFFFFu), v.w & 0x7FFFFFFFu));
+  }
+  if (blockIdx.x == 0)
+    for (size_t i = (n4 << 2) + threadIdx.x; i < n; i += blockDim.x) m = max(m, __float_as_uint(x[i]) & 0x7FFFFFFFu);
+  m = __reduce_max_sync(0xFFFFFFFFu, m);
+  if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(slots + blockIdx.y, m);
+}
+
+// One-time fp16 split of a frozen weight: hi = fp16(w s), lo = fp16(w s - hi).
+__global__ void split_f16_kernel(const float* __restrict__ w, __half* __restrict__ hi, __half* __restrict__ lo,
+                                 size_t n, float s) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float x = w[i] * s;
+    const __half h = __float2half_rn(x);
+    hi[i] = h;
+    lo[i] = __float2half_rn(x - __half2float(h));
+  }
+}
+
 // ------------------------------------------ attention forward: scores + causal softmax -> P
 // One CTA owns 128 query rows of one (batch item, head): the scaled scores of those rows
 // against every key up to the diagonal, (i + 1) * 128 columns, accumulate in TMEM (all 512
@@ -1288,14 +1667,15 @@ EncodeFn encode_fn() {
 // 2-D f32 row-major tensor [rows, cols] (cols contiguous), box [box_rows, box_cols], 128-byte swizzle
 // (box_cols = 32) or none.
 bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
-              uint32_t box_cols, int swizzle_bytes) {
+              uint32_t box_cols, int swizzle_bytes, bool f16 = false) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 4};
+  const cuuint64_t strides[1] = {cols * (f16 ? 2u : 4u)};
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+  return fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr),
+            dims, strides, box, elem,
             CU_TENSOR_MAP_INTERLEAVE_NONE,
             swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                  : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
@@ -1309,7 +1689,11 @@ struct TcState {
   bool usable = true;
   float* rank_scratch = nullptr;
   int pair_clusters = 0;          // resident clusters of the pair kernel on this device (0 = not queried yet)
+  int pair_f16_clusters = 0;
   std::map<const float*, float*> lo_copies;   // frozen B operand -> its precomputed lo part (x - tf32(x))
+  struct F16Copy { __half* hi; __half* lo; int exp; };
+  std::map<const float*, F16Copy> f16_copies; // frozen B operand -> fp16 split of w * 2^exp (F16X2 mode)
+  uint32_t* absmax_dev = nullptr;             // four max|x| slots for the run-time operands of an F16X2 launch
   std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> maps;
   std::set<const void*> smem_attr_done;   // kernels whose dynamic shared-memory limit was raised on this context's device
 };
@@ -1333,6 +1717,16 @@ const CUtensorMap* cached_map(TcState& st, const void* ptr, uint64_t rows, uint6
   return &st.maps.emplace(key, m).first->second;
 }
 
+// fp16 [rows, cols] row-major: box of box_rows x 32 elements (64-byte rows, 64-byte swizzle).
+const CUtensorMap* cached_map_f16(TcState& st, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  const auto key = std::make_tuple(ptr, rows, cols, box_rows, 0x20000u);
+  auto it = st.maps.find(key);
+  if (it != st.maps.end()) return &it->second;
+  CUtensorMap m;
+  if (!make_map(&m, ptr, rows, cols, box_rows, 32, 64, true)) return nullptr;
+  return &st.maps.emplace(key, m).first->second;
+}
+
 // cudaFuncSetAttribute applies to the current device only, so the "already raised" note is kept
 // per context (a process may hold contexts on several GPUs).
 template <class K>
@@ -1350,7 +1744,7 @@ bool ensure_smem_attr(TcState& st, K kern, int bytes) {
 }  // namespace
 
 bool gemm_tc_shape_ok(const seeml_b200_ctx* c, uint64_t M, uint64_t N, uint64_t K) {
-  if (c->gemm_kind == SEEML_B200_GEMM_FP32_SIMT || c->gemm_kind == SEEML_B200_GEMM_BF16) return false;
+  if (c->gemm_kind == SEEML_B200_GEMM_FP32_SIMT) return false;
   if (M < 128 || N < 64 || K < 32) return false;
   if (K % 4 != 0 || N % 4 != 0) return false;              // 16-byte global strides for TMA
   if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return false;
@@ -1433,6 +1827,75 @@ int launch_pair(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   return 1;
 }
 
+// The CTA-pair kernel with the two-term fp16 split. Same shape rule as launch_pair.
+int launch_pair_f16(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
+  if (!ensure_smem_attr(st, gemm_tc_pair_f16_kernel, PairF16Smem::kTotal)) return -1;
+  if (!st.absmax_dev) {
+    if (cudaMalloc(&st.absmax_dev, 64) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+  }
+  const CUtensorMap* ma = cached_map(st, g.A, g.M, g.K, BM);
+  const CUtensorMap* mb = cached_map(st, g.Bt, g.N, g.K, 128);
+  const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
+  const CUtensorMap* ma2 = g.K2 ? cached_map(st, g.A2, g.M, g.K2, BM) : ma;
+  const CUtensorMap* mb2 = g.K2 ? cached_map(st, g.B2t, g.N, g.K2, 128) : mb;
+  const CUtensorMap *mbh = mb, *mbl = mb;
+  int b_pre = 0, eb = 0;
+  auto it = st.f16_copies.find(g.Bt);
+  if (it != st.f16_copies.end()) {
+    mbh = cached_map_f16(st, it->second.hi, g.N, g.K, 128);
+    mbl = cached_map_f16(st, it->second.lo, g.N, g.K, 128);
+    b_pre = 1;
+    eb = it->second.exp;
+  }
+  if (!ma || !mb || !mc || !ma2 || !mb2 || !mbh || !mbl) return -1;
+  // max|x| of the operands converted inside the kernel
+  AbsmaxArgs aa{};
+  aa.ptr[0] = g.A; aa.n[0] = g.M * g.K;
+  if (!b_pre) { aa.ptr[1] = g.Bt; aa.n[1] = g.N * g.K; }
+  if (g.K2) { aa.ptr[2] = g.A2; aa.n[2] = g.M * g.K2; aa.ptr[3] = g.B2t; aa.n[3] = g.N * g.K2; }
+  if (cudaMemsetAsync(st.absmax_dev, 0, 16, c->stream) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  const uint64_t big = std::max<uint64_t>(aa.n[0], aa.n[1]);
+  const unsigned blocks = (unsigned)std::min<uint64_t>(592, (big / 4 + 1023) / 1024 + 1);
+  absmax4_kernel<<<dim3(blocks, 4), 256, 0, c->stream>>>(aa, st.absmax_dev);
+  F16Params p{};
+  p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.K2 = (int)g.K2;
+  p.bias = g.bias; p.addend = g.addend; p.act = g.act; p.alpha = g.alpha == 0.0f ? 1.0f : g.alpha;
+  p.b_pre = b_pre; p.eb_pre = eb; p.absmax = st.absmax_dev; p.err = st.err_dev;
+  p.n_tiles = (int)((g.N + 255) / 256);
+  p.total_tiles = p.n_tiles * (int)(((g.M + BM - 1) / BM) / 2);
+  cudaLaunchConfig_t cfg{};
+  cfg.blockDim = dim3(kThreadsV2);
+  cfg.dynamicSmemBytes = PairF16Smem::kTotal;
+  cfg.stream = c->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (st.pair_f16_clusters == 0) {
+    cfg.gridDim = dim3(2u * 1024u);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_f16_kernel, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 74;
+    }
+    st.pair_f16_clusters = n;
+  }
+  cfg.gridDim = dim3(2u * (unsigned)std::min(p.total_tiles, st.pair_f16_clusters));
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_pair_f16_kernel, *ma, *mb, *mc, *ma2, *mb2, *mbh, *mbl, p);
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return 1;
+}
+
 TcState* state_of(seeml_b200_ctx* c, bool create) {
   auto it = states().find(c);
   if (it == states().end()) {
@@ -1460,12 +1923,13 @@ int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g) {
     return 0;
   TcState* st = state_of(c, false);
   if (!st || !st->usable || !st->err_dev) return 0;
-  const bool split = c->gemm_kind == SEEML_B200_GEMM_TF32X3;
+  const bool split = kind_x3(c);
   int r;
   static const bool half_blocks = [] { const char* e = std::getenv("SEEML_B200_GEMM_KB"); return e && std::atoi(e) == 16; }();
   static const bool pairs = [] { const char* e = std::getenv("SEEML_B200_GEMM_PAIR"); return !e || std::atoi(e) != 0; }();
   const uint64_t m_tiles = (g.M + BM - 1) / BM;
-  if (g.N >= 192 && split && pairs && m_tiles % 2 == 0) r = launch_pair(c, *st, g);
+  if (g.N >= 192 && pairs && m_tiles % 2 == 0 && c->gemm_kind == SEEML_B200_GEMM_F16X2) r = launch_pair_f16(c, *st, g);
+  else if (g.N >= 192 && split && pairs && m_tiles % 2 == 0) r = launch_pair(c, *st, g);
   else if (g.N >= 192 && split && half_blocks) r = launch_tc<256, true, 4, 16>(c, *st, g);
   else if (g.N >= 192) r = split ? launch_tc<256, true, 2>(c, *st, g) : launch_tc<256, false, 4>(c, *st, g);
   else r = split ? launch_tc<128, true, 3>(c, *st, g) : launch_tc<128, false, 6>(c, *st, g);
@@ -1491,7 +1955,7 @@ int launch_bg(seeml_b200_ctx* c, TcState& st, const TcBatched& g) {
   for (int i = 0; i < 2; ++i) {
     p.ax[i] = g.ax[i]; p.ay[i] = g.ay[i]; p.bx[i] = g.bx[i]; p.by[i] = g.by[i]; p.cx[i] = g.cx[i]; p.cy[i] = g.cy[i];
   }
-  p.x3 = c->gemm_kind == SEEML_B200_GEMM_TF32X3;
+  p.x3 = kind_x3(c);
   p.err = st.err_dev;
   const int m_tiles = g.M / BM;
   p.pair_m = ((g.causal == 2 || g.causal == 3) && m_tiles % 2 == 0) ? m_tiles : 0;
@@ -1505,7 +1969,7 @@ int launch_bg(seeml_b200_ctx* c, TcState& st, const TcBatched& g) {
 // Batched per-head product on the tensor cores. 1 = launched, 0 = shape / context not
 // eligible (the caller's CUDA-core path runs instead).
 int gemm_tc_batched(seeml_b200_ctx* c, const TcBatched& g) {
-  if (c->gemm_kind != SEEML_B200_GEMM_TF32X3 && c->gemm_kind != SEEML_B200_GEMM_TF32) return 0;
+  if (!kind_tc(c)) return 0;
   if (g.M % BM != 0 || g.N % 64 != 0 || g.K % BK != 0 || g.M <= 0 || g.N <= 0 || g.K <= 0) return 0;
   if (g.batch <= 0 || g.batch > 65535 || g.H <= 0) return 0;
   if ((g.a_cols | g.b_cols | g.c_cols) % 4 != 0) return 0;
@@ -1531,7 +1995,7 @@ int gemm_tc_batched(seeml_b200_ctx* c, const TcBatched& g) {
 // A once through a deep TMA ring (HBM-bound). 1 = launched, 0 = not eligible.
 int gemm_tc_rank_n(seeml_b200_ctx* c, const float* A, const float* Bnk, float* out, uint64_t M, uint64_t n,
                    uint64_t K, float alpha) {
-  if (c->gemm_kind != SEEML_B200_GEMM_TF32X3 && c->gemm_kind != SEEML_B200_GEMM_TF32) return 0;
+  if (!kind_tc(c)) return 0;
   if ((n != 16 && n != 32 && n != 64) || M < 1024 || K < 128 || K % 4 != 0) return 0;
   if (M > 0x7FFFFFFF || K > 0x7FFFFFFF) return 0;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bnk) | reinterpret_cast<uintptr_t>(out)) & 15) return 0;
@@ -1539,7 +2003,7 @@ int gemm_tc_rank_n(seeml_b200_ctx* c, const float* A, const float* Bnk, float* o
   if (!st || !st->usable || !st->err_dev) return 0;
   TcGemm g{};
   g.A = A; g.Bt = Bnk; g.C = out; g.M = M; g.N = n; g.K = K; g.alpha = alpha;
-  const bool split = c->gemm_kind == SEEML_B200_GEMM_TF32X3;
+  const bool split = kind_x3(c);
   int r;
   if (n == 16) r = split ? launch_tc<16, true, 6>(c, *st, g) : launch_tc<16, false, 8>(c, *st, g);
   else if (n == 32) r = split ? launch_tc<32, true, 5>(c, *st, g) : launch_tc<32, false, 8>(c, *st, g);
@@ -1587,7 +2051,7 @@ uint64_t gemm_tc_rank_tn_chunk_rows(uint64_t T, uint64_t big, uint64_t small) {
 // memory. The caller sums the chunks in order. 1 = launched, 0 = not eligible.
 int gemm_tc_rank_tn(seeml_b200_ctx* c, const float* W, const float* S, float* partial, uint64_t T, uint64_t big,
                     uint64_t small, uint64_t chunk_rows) {
-  if (c->gemm_kind != SEEML_B200_GEMM_TF32X3 && c->gemm_kind != SEEML_B200_GEMM_TF32) return 0;
+  if (!kind_tc(c)) return 0;
   if (chunk_rows == 0 || T % chunk_rows != 0 || chunk_rows % BK != 0) return 0;
   const uint64_t chunks = T / chunk_rows;
   if (chunks > 65535 || chunks * big > 0x7FFFFFFF || T > 0x7FFFFFFF) return 0;
@@ -1618,7 +2082,7 @@ int gemm_tc_rank_tn(seeml_b200_ctx* c, const float* W, const float* S, float* pa
 // A and B are [B*S, H*64]; out / Pin are [B*H*S, S]. 1 = launched, 0 = not eligible.
 static int attn_rows_launch(seeml_b200_ctx* c, int mode, const float* A, const float* Bm, const float* Pin, float* out,
                             uint64_t B, uint64_t S, uint64_t H, uint64_t dh, float alpha) {
-  if (c->gemm_kind != SEEML_B200_GEMM_TF32X3 && c->gemm_kind != SEEML_B200_GEMM_TF32) return 0;
+  if (!kind_tc(c)) return 0;
   if (dh != 64 || S % BM != 0 || S > 512 || B * H == 0 || B * H > 65535) return 0;
   if ((B * S) >> 31 || (H * dh) >> 31 || (B * H * S) >> 31) return 0;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bm) | reinterpret_cast<uintptr_t>(out) |
@@ -1640,7 +2104,7 @@ static int attn_rows_launch(seeml_b200_ctx* c, int mode, const float* A, const f
   p.S = (int)S; p.H = (int)H; p.alpha = alpha;
   p.qx[0] = 0; p.qx[1] = (int)dh; p.qy[0] = (int)S; p.qy[1] = 0;
   p.pin = Pin;
-  p.x3 = c->gemm_kind == SEEML_B200_GEMM_TF32X3; p.err = st->err_dev;
+  p.x3 = kind_x3(c); p.err = st->err_dev;
   dim3 grid((unsigned)(S / BM), (unsigned)(B * H));
   if (mode == 0) attn_scores_softmax_kernel<0><<<grid, kAfThreads, kSmem, c->stream>>>(*mq, *mk, *mp, p);
   else attn_scores_softmax_kernel<1><<<grid, kAfThreads, kSmem, c->stream>>>(*mq, *mk, *mp, p);
@@ -1655,7 +2119,7 @@ int attn_scores_softmax_tc(seeml_b200_ctx* c, const float* Q, const float* K, fl
   return attn_rows_launch(c, 0, Q, K, nullptr, P, B, S, H, dh, alpha);
 }
 bool attn_rows_eligible(const seeml_b200_ctx* c, uint64_t B, uint64_t S, uint64_t H, uint64_t dh) {
-  return (c->gemm_kind == SEEML_B200_GEMM_TF32X3 || c->gemm_kind == SEEML_B200_GEMM_TF32) && dh == 64 &&
+  return kind_tc(c) && dh == 64 &&
          S % BM == 0 && S <= 512 && B * H > 0 && B * H <= 65535 && !((B * H * S) >> 31);
 }
 int attn_ds_tc(seeml_b200_ctx* c, const float* dO, const float* V, const float* P, float* dS, uint64_t B, uint64_t S,
@@ -1681,15 +2145,49 @@ const float* gemm_tc_transposed_weight(seeml_b200_ctx* c, uint64_t rodata_off, u
   return t;
 }
 
-// Registers a precomputed lo copy for a frozen B operand (device pointer `w`, `elems` floats).
-static int ensure_lo_copy(seeml_b200_ctx* c, const float* w, uint64_t elems) {
+// Registers the precomputed split of a frozen B operand (device pointer `w`, [N, K] floats): the
+// lo part x - tf32(x) for the three-product tf32 kernels, or - in F16X2 mode, for shapes the
+// CTA-pair kernel takes - the fp16 hi / lo copies of w * 2^exp. Failure to allocate is not fatal:
+// the kernels then split the operand themselves.
+static int ensure_lo_copy(seeml_b200_ctx* c, const float* w, uint64_t N, uint64_t K) {
   TcState* st = state_of(c, false);
-  if (!st || c->gemm_kind != SEEML_B200_GEMM_TF32X3) return 0;
+  if (!st || !kind_x3(c)) return 0;
+  const uint64_t elems = N * K;
+  if (c->gemm_kind == SEEML_B200_GEMM_F16X2 && N >= 192 && K % 8 == 0) {
+    if (st->f16_copies.count(w)) return 0;
+    if (!st->absmax_dev && cudaMalloc(&st->absmax_dev, 64) != cudaSuccess) {
+      cudaGetLastError();
+      st->absmax_dev = nullptr;
+      return 0;
+    }
+    __half *hi = nullptr, *lo = nullptr;
+    if (cudaMalloc(&hi, elems * sizeof(__half)) != cudaSuccess || cudaMalloc(&lo, elems * sizeof(__half)) != cudaSuccess) {
+      cudaGetLastError();
+      cudaFree(hi);
+      return 0;
+    }
+    AbsmaxArgs aa{};
+    aa.ptr[0] = w; aa.n[0] = elems;
+    uint32_t bits = 0;
+    cudaMemsetAsync(st->absmax_dev, 0, 16, c->stream);
+    absmax4_kernel<<<dim3(592, 1), 256, 0, c->stream>>>(aa, st->absmax_dev);
+    cudaMemcpyAsync(&bits, st->absmax_dev, 4, cudaMemcpyDeviceToHost, c->stream);
+    if (cudaStreamSynchronize(c->stream) != cudaSuccess) {
+      cudaGetLastError();
+      cudaFree(hi);
+      cudaFree(lo);
+      return 0;
+    }
+    const int e = f16_scale_exp(bits);
+    split_f16_kernel<<<1184, 256, 0, c->stream>>>(w, hi, lo, (size_t)elems, std::ldexp(1.0f, e));
+    st->f16_copies[w] = TcState::F16Copy{hi, lo, e};
+    return 0;
+  }
   if (st->lo_copies.count(w)) return 0;
   float* lo = nullptr;
   if (cudaMalloc(&lo, elems * sizeof(float)) != cudaSuccess) {
     cudaGetLastError();
-    return 0;                                   // not fatal: the kernel derives the lo tiles itself
+    return 0;
   }
   lo_copy_kernel<<<1184, 256, 0, c->stream>>>(w, lo, (size_t)elems);
   st->lo_copies[w] = lo;
@@ -1703,15 +2201,15 @@ static bool tc_instr(const seeml_b200_ctx* c, const Instr& ins) {
 }
 
 int gemm_tensor_core_prepare(seeml_b200_ctx* c, const Instr& ins) {
-  if (c->gemm_kind == SEEML_B200_GEMM_FP32_SIMT || c->gemm_kind == SEEML_B200_GEMM_BF16) return 0;
+  if (c->gemm_kind == SEEML_B200_GEMM_FP32_SIMT) return 0;
   if (!state_of(c, true)) return cuda_fail(cudaGetLastError(), "tc error word");
   if (!tc_instr(c, ins)) return 0;
   if (ins.opcode == kGemmNN) {
     const float* wt = gemm_tc_transposed_weight(c, ref_off(ins.in[1]), ins.out[2], ins.out[1], true);
     if (!wt) return fail("UpdateEngine: transposed weight allocation failed");
-    ensure_lo_copy(c, wt, ins.out[1] * ins.out[2]);
+    ensure_lo_copy(c, wt, ins.out[1], ins.out[2]);
   } else if (is_rodata(ins.in[1])) {
-    ensure_lo_copy(c, reinterpret_cast<const float*>(c->rodata + ref_off(ins.in[1])), ins.out[1] * ins.out[2]);
+    ensure_lo_copy(c, reinterpret_cast<const float*>(c->rodata + ref_off(ins.in[1])), ins.out[1], ins.out[2]);
   }
   return 0;
 }
@@ -1754,6 +2252,11 @@ void gemm_tensor_core_release(seeml_b200_ctx* c) {
   cudaFree(sit->second.err_dev);
   cudaFree(sit->second.rank_scratch);
   for (auto& kv : sit->second.lo_copies) cudaFree(kv.second);
+  for (auto& kv : sit->second.f16_copies) {
+    cudaFree(kv.second.hi);
+    cudaFree(kv.second.lo);
+  }
+  cudaFree(sit->second.absmax_dev);
   states().erase(sit);
 }
 

@@ -118,6 +118,14 @@ __device__ __forceinline__ void mma_tf32_pair(uint32_t tmem_d, uint64_t da, uint
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
       : "memory");
 }
+__device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+      : "memory");
+}
 // Completion of the pair's MMAs arrives on the barrier at this offset in both CTAs (mask 0b11).
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
   asm volatile(
@@ -187,7 +195,10 @@ __device__ __forceinline__ uint64_t smem_desc_k(uint32_t addr) {
 __host__ __device__ constexpr uint32_t idesc_tf32(int m, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-
+// Instruction descriptor, kind::f16 with fp16 operands (format code 0) and an f32 accumulator.
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
 
 }  // namespace tc
 }  // namespace seeml_b200

@@ -15,7 +15,7 @@ from . import _lib as L
 from .formats import PlanHeader, parse_plan
 
 MODE_CONTRACT, MODE_FUSED = 0, 1
-GEMM_TF32X3, GEMM_BF16, GEMM_FP32_SIMT, GEMM_TF32 = 0, 1, 2, 3
+GEMM_TF32X3, GEMM_F16X2, GEMM_FP32_SIMT, GEMM_TF32 = 0, 1, 2, 3
 
 
 def _p(a: np.ndarray):
@@ -218,6 +218,9 @@ class UpdateEngine:
         L.check(L.lib().seeml_b200_engine_step_timings(self.h, C.byref(s), C.byref(a), C.byref(b),
                                                        C.byref(c)))
         return s.value, a.value, b.value, c.value
+
+    def reset_step_timings(self):
+        L.check(L.lib().seeml_b200_engine_reset_step_timings(self.h))
 
     def close(self):
         if getattr(self, "h", None):
