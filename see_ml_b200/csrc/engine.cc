@@ -390,17 +390,17 @@ int write_all(int fd, const void* p, size_t n) {
 int write_file_durable(const std::string& path, const void* a, size_t an, const void* b, size_t bn) {
   const std::string tmp = path + ".tmp." + std::to_string(::getpid());
   const int fd = ::open(tmp.c_str(), O_WRONLY | O_CREAT | O_TRUNC, 0644);
-  if (fd < 0) return fail("DurableIo: cannot write '" + tmp + "'");
+  if (fd < 0) return fail("DurableIO: cannot write '" + tmp + "'");
   int bad = write_all(fd, a, an) || (bn && write_all(fd, b, bn));
   if (!bad && ::fsync(fd) != 0) bad = 1;
   ::close(fd);
   if (bad) {
     ::unlink(tmp.c_str());
-    return fail("DurableIo: short write to '" + tmp + "'");
+    return fail("DurableIO: short write to '" + tmp + "'");
   }
   if (std::rename(tmp.c_str(), path.c_str()) != 0) {
     ::unlink(tmp.c_str());
-    return fail("DurableIo: cannot rename '" + tmp + "' into place");
+    return fail("DurableIO: cannot rename '" + tmp + "' into place");
   }
   return 0;
 }
@@ -670,14 +670,14 @@ int seeml_b200_engine_verify_source_model(seeml_b200_engine* e, const char* path
   if (!e || !e->loaded || !path) return fail("UpdateEngine: no plan loaded");
   if (e->L.h.source_model_hash == 0) return 0;
   std::FILE* f = std::fopen(path, "rb");
-  if (!f) return fail(std::string("DurableIo: cannot open '") + path + "'");
+  if (!f) return fail(std::string("DurableIO: cannot open '") + path + "'");
   std::fseek(f, 0, SEEK_END);
   const long n = std::ftell(f);
   std::fseek(f, 0, SEEK_SET);
   std::vector<uint8_t> bytes(n > 0 ? (size_t)n : 0);
   const size_t got = bytes.empty() ? 0 : std::fread(bytes.data(), 1, bytes.size(), f);
   std::fclose(f);
-  if (got != bytes.size()) return fail(std::string("DurableIo: cannot read '") + path + "'");
+  if (got != bytes.size()) return fail(std::string("DurableIO: cannot read '") + path + "'");
   if (content_hash64(bytes.data(), bytes.size()) != e->L.h.source_model_hash)
     return fail(std::string("UpdateEngine: source model does not match the plan's source_model_hash — "
                             "refusing to run against '") + path + "'");
@@ -691,23 +691,23 @@ int seeml_b200_engine_commit(seeml_b200_engine* e, const char* src, const char* 
   Loaded& L = e->L;
   const std::string lock_path = std::string(dst) + ".lock";
   const int lock_fd = ::open(lock_path.c_str(), O_RDWR | O_CREAT, 0644);
-  if (lock_fd < 0) return fail("DurableIo: cannot open commit lock '" + lock_path + "'");
+  if (lock_fd < 0) return fail("DurableIO: cannot open commit lock '" + lock_path + "'");
   if (::flock(lock_fd, LOCK_EX) != 0) {
     ::close(lock_fd);
-    return fail("DurableIo: cannot take commit lock '" + lock_path + "'");
+    return fail("DurableIO: cannot take commit lock '" + lock_path + "'");
   }
   int rc = 0;
   std::vector<uint8_t> bytes;
   {
     std::FILE* f = std::fopen(src, "rb");
-    if (!f) rc = fail(std::string("DurableIo: cannot open '") + src + "'");
+    if (!f) rc = fail(std::string("DurableIO: cannot open '") + src + "'");
     if (!rc) {
       std::fseek(f, 0, SEEK_END);
       const long n = std::ftell(f);
       std::fseek(f, 0, SEEK_SET);
       bytes.resize(n > 0 ? (size_t)n : 0);
       if (!bytes.empty() && std::fread(bytes.data(), 1, bytes.size(), f) != bytes.size())
-        rc = fail(std::string("DurableIo: cannot read '") + src + "'");
+        rc = fail(std::string("DurableIO: cannot read '") + src + "'");
       std::fclose(f);
     }
   }
