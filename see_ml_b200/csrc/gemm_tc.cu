@@ -958,11 +958,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
 // worker warps. max|x| of the run-time operands is measured by absmax4_kernel just before.
 constexpr int kF16Raw = BM * 32 * 4;       // a 128 x 32 f32 tile
 constexpr int kF16Half = BM * 32 * 2;      // the same tile in fp16: 64-byte rows
+constexpr int kF16Stages = 4;
 struct PairF16Smem {
   static constexpr int kARaw = 0, kAHi = kF16Raw, kALo = kAHi + kF16Half, kBHi = kALo + kF16Half,
-                       kBLo = kBHi + kF16Half, kBRaw = kBLo + kF16Half;
-  static constexpr int kStage = kBRaw + kF16Raw;                   // 64 KiB
-  static constexpr int kTotal = kPairStages * kStage + 256 + 1024;
+                       kBLo = kBHi + kF16Half;
+  static constexpr int kStage = kBLo + kF16Half;                   // 48 KiB
+  static constexpr int kTotal = kF16Stages * kStage + 256 + 1024;
 };
 struct F16Params {
   int M, N, K, K2;
@@ -970,9 +971,9 @@ struct F16Params {
   const float* addend;
   int act;
   float alpha;
-  int b_pre;                // the main pair's B tiles come pre-split through mapBhi / mapBlo
-  int eb_pre;               // scale exponent of those copies: they hold the split of w * 2^eb_pre
-  const uint32_t* absmax;   // device: bit patterns of max|x| over A, B, A2, B2 (B unused when b_pre)
+  int eb_pre;               // scale exponent of the frozen B copies: they hold the split of w * 2^eb_pre
+  const uint32_t* absmax;   // device: bit patterns of max|x| over A, -, A2, B2
+  int dbg;                  // measurement switches (0 in production): 1 = workers skip the conversion, 2 = one product
   int n_tiles, total_tiles;
   int* err;
 };
@@ -987,6 +988,18 @@ __host__ __device__ __forceinline__ int f16_scale_exp(uint32_t bits) {
 }
 __device__ __forceinline__ float pow2i(int e) { return __int_as_float((e + 127) << 23); }
 
+// hi = x rounded to 11 significant bits (what an fp16 keeps), by Veltkamp's splitting with plain
+// f32 arithmetic, and lo = x - hi (exact). Both then convert to fp16 two at a time. For |x| below
+// fp16's normal range (2^-14) the conversion of hi rounds once more, by at most 2^-25.
+__device__ __forceinline__ void split11(float x, float& hi, float& lo) {
+  const float t = __fmul_rn(x, 8193.0f);          // 2^13 + 1
+  hi = __fsub_rn(t, __fsub_rn(t, x));
+  lo = __fsub_rn(x, hi);
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
 // 128 rows x 32 f32 in the 128-byte swizzled layout of a TMA load -> the hi and lo fp16 tiles,
 // 64-byte rows in the 64-byte swizzled K-major layout the MMA reads.
 __device__ __forceinline__ void split_f16_tile(const uint8_t* raw, uint8_t* hi, uint8_t* lo, float sc, int t) {
@@ -994,28 +1007,24 @@ __device__ __forceinline__ void split_f16_tile(const uint8_t* raw, uint8_t* hi, 
   for (int i = t; i < kF16Raw / 16; i += kWorkers) {
     const int row = i >> 3, c = (i & 7) ^ (row & 7);          // logical 16-byte chunk: k = 4c .. 4c+3
     const float4 v = reinterpret_cast<const float4*>(raw)[i];
-    const float x0 = v.x * sc, x1 = v.y * sc, x2 = v.z * sc, x3 = v.w * sc;
-    const __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1), h2 = __float2half_rn(x2), h3 = __float2half_rn(x3);
-    const __half l0 = __float2half_rn(x0 - __half2float(h0)), l1 = __float2half_rn(x1 - __half2float(h1));
-    const __half l2 = __float2half_rn(x2 - __half2float(h2)), l3 = __float2half_rn(x3 - __half2float(h3));
+    float h0, h1, h2, h3, l0, l1, l2, l3;
+    split11(v.x * sc, h0, l0);
+    split11(v.y * sc, h1, l1);
+    split11(v.z * sc, h2, l2);
+    split11(v.w * sc, h3, l3);
     const int off = row * 64 + ((((c >> 1) ^ (row >> 1)) & 3) << 4) + ((c & 1) << 3);
-    uint2 hv, lv;
-    hv.x = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
-    hv.y = (uint32_t)__half_as_ushort(h2) | ((uint32_t)__half_as_ushort(h3) << 16);
-    lv.x = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
-    lv.y = (uint32_t)__half_as_ushort(l2) | ((uint32_t)__half_as_ushort(l3) << 16);
-    *reinterpret_cast<uint2*>(hi + off) = hv;
-    *reinterpret_cast<uint2*>(lo + off) = lv;
+    *reinterpret_cast<uint2*>(hi + off) = make_uint2(pack_h2(h0, h1), pack_h2(h2, h3));
+    *reinterpret_cast<uint2*>(lo + off) = make_uint2(pack_h2(l0, l1), pack_h2(l2, l3));
   }
 }
 
 __global__ void __launch_bounds__(kThreadsV2, 1)
-gemm_tc_pair_f16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                        const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapA2,
-                        const __grid_constant__ CUtensorMap mapB2, const __grid_constant__ CUtensorMap mapBhi,
-                        const __grid_constant__ CUtensorMap mapBlo, F16Params p) {
+gemm_tc_pair_f16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapA2,
+                        const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapBhi,
+                        const __grid_constant__ CUtensorMap mapBlo, const __grid_constant__ CUtensorMap mapB2hi,
+                        const __grid_constant__ CUtensorMap mapB2lo, F16Params p) {
   using S = PairF16Smem;
-  constexpr int STAGES = kPairStages, BN = 256, KB = 32;
+  constexpr int STAGES = kF16Stages, BN = 256, KB = 32;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -1089,18 +1098,15 @@ gemm_tc_pair_f16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
           }
           if (!ok) break;
           const uint32_t stg = base + s * S::kStage;
-          mbar_expect_tx(bar_full(s), 2 * kF16Raw);          // A raw + (B hi + B lo | B raw): 32 KiB either way
+          mbar_expect_tx(bar_full(s), kF16Raw + 2 * kF16Half);          // A raw + B hi + B lo
           if (kb < nkb1) {
             tma_load_2d(stg + S::kARaw, &mapA, bar_full(s), kb * KB, m0);
-            if (p.b_pre) {
-              tma_load_2d(stg + S::kBHi, &mapBhi, bar_full(s), kb * KB, nb);
-              tma_load_2d(stg + S::kBLo, &mapBlo, bar_full(s), kb * KB, nb);
-            } else {
-              tma_load_2d(stg + S::kBRaw, &mapB, bar_full(s), kb * KB, nb);
-            }
+            tma_load_2d(stg + S::kBHi, &mapBhi, bar_full(s), kb * KB, nb);
+            tma_load_2d(stg + S::kBLo, &mapBlo, bar_full(s), kb * KB, nb);
           } else {
             tma_load_2d(stg + S::kARaw, &mapA2, bar_full(s), (kb - nkb1) * KB, m0);
-            tma_load_2d(stg + S::kBRaw, &mapB2, bar_full(s), (kb - nkb1) * KB, nb);
+            tma_load_2d(stg + S::kBHi, &mapB2hi, bar_full(s), (kb - nkb1) * KB, nb);
+            tma_load_2d(stg + S::kBLo, &mapB2lo, bar_full(s), (kb - nkb1) * KB, nb);
           }
         }
         if (ok && pend >= 0) {
@@ -1143,8 +1149,10 @@ gemm_tc_pair_f16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
           const uint64_t da = smem_desc_sw64(stg + S::kAHi + kk * 32), dal = smem_desc_sw64(stg + S::kALo + kk * 32);
           const uint64_t db = smem_desc_sw64(stg + S::kBHi + kk * 32), dbl = smem_desc_sw64(stg + S::kBLo + kk * 32);
           mma_f16_pair(tmem_d, da, db, idesc, (j | kk) != 0);
-          mma_f16_pair(tmem_d, dal, db, idesc, 1);
-          mma_f16_pair(tmem_d, da, dbl, idesc, 1);
+          if (!(p.dbg & 2)) {
+            mma_f16_pair(tmem_d, dal, db, idesc, 1);
+            mma_f16_pair(tmem_d, da, dbl, idesc, 1);
+          }
         }
         mma_commit_pair(bar_empty(s));
         if (last) {
@@ -1158,9 +1166,9 @@ gemm_tc_pair_f16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
     const int t = threadIdx.x - 64;
     const int q = warp & 3, half = (warp - 2) >> 2, row0 = q * 32;
     constexpr int NH = BN / 2, LD = 32;
-    const int ea = f16_scale_exp(p.absmax[0]), eb = p.b_pre ? p.eb_pre : f16_scale_exp(p.absmax[1]);
+    const int ea = f16_scale_exp(p.absmax[0]), eb = p.eb_pre;
     const int ea2 = f16_scale_exp(p.absmax[2]), eb2 = f16_scale_exp(p.absmax[3]);
-    const float sa = pow2i(ea), sb = pow2i(eb), sa2 = pow2i(ea2), sb2 = pow2i(eb2);
+    const float sa = pow2i(ea), sa2 = pow2i(ea2);
     const float cs_main = pow2i(-ea) * pow2i(-eb), cs_tail = pow2i(-ea2) * pow2i(-eb2);
     float acc[NH];
     bool ok = true;
@@ -1203,9 +1211,7 @@ gemm_tc_pair_f16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
       ok = mbar_wait(bar_full(s), r & 1, p.err, 43);
       if (!ok) break;
       uint8_t* stg = base_ptr + s * S::kStage;
-      const bool main_blk = kb < nkb1;
-      split_f16_tile(stg + S::kARaw, stg + S::kAHi, stg + S::kALo, main_blk ? sa : sa2, t);
-      if (!(p.b_pre && main_blk)) split_f16_tile(stg + S::kBRaw, stg + S::kBHi, stg + S::kBLo, main_blk ? sb : sb2, t);
+      if (!(p.dbg & 1)) split_f16_tile(stg + S::kARaw, stg + S::kAHi, stg + S::kALo, kb < nkb1 ? sa : sa2, t);
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(bar_split(s), 0);
@@ -1303,11 +1309,25 @@ __global__ void __launch_bounds__(256) absmax4_kernel(AbsmaxArgs a, uint32_t* __
 __global__ void split_f16_kernel(const float* __restrict__ w, __half* __restrict__ hi, __half* __restrict__ lo,
                                  size_t n, float s) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const float x = w[i] * s;
-    const __half h = __float2half_rn(x);
-    hi[i] = h;
-    lo[i] = __float2half_rn(x - __half2float(h));
+    float h, l;
+    split11(w[i] * s, h, l);
+    hi[i] = __float2half_rn(h);
+    lo[i] = __float2half_rn(l);
   }
+}
+
+// The low-rank tail's B operand ([N, K2] f32, K2 <= 32, rewritten every step) as fp16 hi / lo
+// tiles [N, 32] (zero-padded along K), scaled by the power of two its measured max|x| asks for.
+__global__ void split_f16_tail_kernel(const float* __restrict__ b, __half* __restrict__ hi, __half* __restrict__ lo,
+                                      int N, int K2, const uint32_t* __restrict__ absmax_slot) {
+  const float s = pow2i(f16_scale_exp(*absmax_slot));
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N * 32) return;
+  const int n = i >> 5, k = i & 31;
+  float h = 0.0f, l = 0.0f;
+  if (k < K2) split11(b[(size_t)n * K2 + k] * s, h, l);
+  hi[i] = __float2half_rn(h);
+  lo[i] = __float2half_rn(l);
 }
 
 // ------------------------------------------ attention forward: scores + causal softmax -> P
@@ -1683,6 +1703,7 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, u
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+constexpr uint64_t kF16TailRows = 65536;    // widest N the F16X2 tail scratch holds
 struct TcState {
   int* err_dev = nullptr;
   bool attrs_set = false;
@@ -1694,6 +1715,7 @@ struct TcState {
   struct F16Copy { __half* hi; __half* lo; int exp; };
   std::map<const float*, F16Copy> f16_copies; // frozen B operand -> fp16 split of w * 2^exp (F16X2 mode)
   uint32_t* absmax_dev = nullptr;             // four max|x| slots for the run-time operands of an F16X2 launch
+  __half *tail_hi = nullptr, *tail_lo = nullptr;   // fp16 tiles of the low-rank tail's B operand, [kF16TailRows, 32] each
   std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> maps;
   std::set<const void*> smem_attr_done;   // kernels whose dynamic shared-memory limit was raised on this context's device
 };
@@ -1827,46 +1849,49 @@ int launch_pair(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   return 1;
 }
 
-// The CTA-pair kernel with the two-term fp16 split. Same shape rule as launch_pair.
+// The CTA-pair kernel with the two-term fp16 split. Same shape rule as launch_pair; the main
+// pair's B must be a frozen operand with fp16 copies (made at build time) and the tail at most 32
+// wide, otherwise the three-product tf32 kernel takes the launch.
 int launch_pair_f16(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
+  auto it = st.f16_copies.find(g.Bt);
+  if (it == st.f16_copies.end() || g.K2 > 32 || g.N > kF16TailRows) return launch_pair(c, st, g);
   if (!ensure_smem_attr(st, gemm_tc_pair_f16_kernel, PairF16Smem::kTotal)) return -1;
-  if (!st.absmax_dev) {
-    if (cudaMalloc(&st.absmax_dev, 64) != cudaSuccess) {
+  if (!st.absmax_dev || !st.tail_hi) {
+    if ((!st.absmax_dev && cudaMalloc(&st.absmax_dev, 64) != cudaSuccess) ||
+        (!st.tail_hi && cudaMalloc(&st.tail_hi, 2 * kF16TailRows * 32 * sizeof(__half)) != cudaSuccess)) {
       cudaGetLastError();
       return -1;
     }
+    st.tail_lo = st.tail_hi + kF16TailRows * 32;
   }
   const CUtensorMap* ma = cached_map(st, g.A, g.M, g.K, BM);
-  const CUtensorMap* mb = cached_map(st, g.Bt, g.N, g.K, 128);
   const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
   const CUtensorMap* ma2 = g.K2 ? cached_map(st, g.A2, g.M, g.K2, BM) : ma;
-  const CUtensorMap* mb2 = g.K2 ? cached_map(st, g.B2t, g.N, g.K2, 128) : mb;
-  const CUtensorMap *mbh = mb, *mbl = mb;
-  int b_pre = 0, eb = 0;
-  auto it = st.f16_copies.find(g.Bt);
-  if (it != st.f16_copies.end()) {
-    mbh = cached_map_f16(st, it->second.hi, g.N, g.K, 128);
-    mbl = cached_map_f16(st, it->second.lo, g.N, g.K, 128);
-    b_pre = 1;
-    eb = it->second.exp;
-  }
-  if (!ma || !mb || !mc || !ma2 || !mb2 || !mbh || !mbl) return -1;
-  // max|x| of the operands converted inside the kernel
+  const CUtensorMap* mbh = cached_map_f16(st, it->second.hi, g.N, g.K, 128);
+  const CUtensorMap* mbl = cached_map_f16(st, it->second.lo, g.N, g.K, 128);
+  const CUtensorMap* mb2h = g.K2 ? cached_map_f16(st, st.tail_hi, g.N, 32, 128) : mbh;
+  const CUtensorMap* mb2l = g.K2 ? cached_map_f16(st, st.tail_lo, g.N, 32, 128) : mbl;
+  if (!ma || !mc || !ma2 || !mbh || !mbl || !mb2h || !mb2l) return -1;
+  static const int dbg = [] { const char* e = std::getenv("SEEML_B200_F16_DBG"); return e ? std::atoi(e) : 0; }();
+  // max|x| of the operands converted at run time, then the tail's B as fp16 tiles
   AbsmaxArgs aa{};
   aa.ptr[0] = g.A; aa.n[0] = g.M * g.K;
-  if (!b_pre) { aa.ptr[1] = g.Bt; aa.n[1] = g.N * g.K; }
   if (g.K2) { aa.ptr[2] = g.A2; aa.n[2] = g.M * g.K2; aa.ptr[3] = g.B2t; aa.n[3] = g.N * g.K2; }
-  if (cudaMemsetAsync(st.absmax_dev, 0, 16, c->stream) != cudaSuccess) {
-    cudaGetLastError();
-    return -1;
+  if (!(dbg & 4)) {
+    if (cudaMemsetAsync(st.absmax_dev, 0, 16, c->stream) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+    const unsigned blocks = (unsigned)std::min<uint64_t>(592, (aa.n[0] / 4 + 1023) / 1024 + 1);
+    absmax4_kernel<<<dim3(blocks, g.K2 ? 4 : 1), 256, 0, c->stream>>>(aa, st.absmax_dev);
   }
-  const uint64_t big = std::max<uint64_t>(aa.n[0], aa.n[1]);
-  const unsigned blocks = (unsigned)std::min<uint64_t>(592, (big / 4 + 1023) / 1024 + 1);
-  absmax4_kernel<<<dim3(blocks, 4), 256, 0, c->stream>>>(aa, st.absmax_dev);
+  if (g.K2)
+    split_f16_tail_kernel<<<(unsigned)((g.N * 32 + 255) / 256), 256, 0, c->stream>>>(g.B2t, st.tail_hi, st.tail_lo, (int)g.N,
+                                                                                  (int)g.K2, st.absmax_dev + 3);
   F16Params p{};
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.K2 = (int)g.K2;
   p.bias = g.bias; p.addend = g.addend; p.act = g.act; p.alpha = g.alpha == 0.0f ? 1.0f : g.alpha;
-  p.b_pre = b_pre; p.eb_pre = eb; p.absmax = st.absmax_dev; p.err = st.err_dev;
+  p.eb_pre = it->second.exp; p.absmax = st.absmax_dev; p.err = st.err_dev; p.dbg = dbg;
   p.n_tiles = (int)((g.N + 255) / 256);
   p.total_tiles = p.n_tiles * (int)(((g.M + BM - 1) / BM) / 2);
   cudaLaunchConfig_t cfg{};
@@ -1888,7 +1913,7 @@ int launch_pair_f16(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
     st.pair_f16_clusters = n;
   }
   cfg.gridDim = dim3(2u * (unsigned)std::min(p.total_tiles, st.pair_f16_clusters));
-  const cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_pair_f16_kernel, *ma, *mb, *mc, *ma2, *mb2, *mbh, *mbl, p);
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_pair_f16_kernel, *ma, *ma2, *mc, *mbh, *mbl, *mb2h, *mb2l, p);
   if (le != cudaSuccess) {
     cudaGetLastError();
     return -1;
@@ -2257,6 +2282,7 @@ void gemm_tensor_core_release(seeml_b200_ctx* c) {
     cudaFree(kv.second.lo);
   }
   cudaFree(sit->second.absmax_dev);
+  cudaFree(sit->second.tail_hi);
   states().erase(sit);
 }
 

@@ -332,3 +332,72 @@ def test_hundred_step_loss_curve_on_tensor_core_shapes(golden_dir):
         assert res.loss_curve[-1] < 0.7 * res.loss_curve[0]          # it actually learned
         assert abs(res.final_avg_loss - want["final_avg_loss"]) <= 5e-3 * want["final_avg_loss"]
         e.close()
+
+
+def test_step_timing_split_accumulates_and_resets(golden_dir):
+    """StepTimings (update_engine.h:84-89, ResetStepTimings :190): one sample per executed
+    training stream, split at the loss-forward and first-optimiser boundaries; off by default;
+    timed and untimed runs give the same bits."""
+    z, _ = _golden(golden_dir)
+    pc = next(p for p in plancases.plan_cases() if p.name == "llama_tiny")
+    blob = z[pc.name].tobytes()
+    e = _engine(blob, mode=1)
+    ds = pc.dataset()
+    e.train(ds, 3)
+    assert e.step_timings() == (0, 0.0, 0.0, 0.0)
+    e.enable_step_timing(True)
+    e.train(ds, 5)
+    steps, fwd, bwd, opt = e.step_timings()
+    assert steps == 5 and fwd > 0 and bwd > 0 and opt > 0
+    assert fwd + bwd + opt < 5.0          # seconds: five steps of a toy model
+    e.reset_step_timings()
+    assert e.step_timings() == (0, 0.0, 0.0, 0.0)
+    e.enable_step_timing(False)
+    timed = e.arena_read(0, e.header.persistent_size)
+    plain = _engine(blob, mode=1)
+    ds2 = pc.dataset()
+    plain.train(ds2, 8)
+    np.testing.assert_array_equal(timed, plain.arena_read(0, plain.header.persistent_size))
+
+
+def test_larger_program_after_graph_capture_keeps_earlier_graphs_valid():
+    """A context's captured range graphs hold the addresses of its scratch buffers; building a
+    program that needs more scratch replaces those buffers, so the graphs must be dropped and
+    recaptured, never replayed against freed memory."""
+    import opcases
+    from see_ml_b200.engine import Context
+    from see_ml_b200.formats import Op
+    rng = np.random.default_rng(12)
+    rows, classes = 64, 40
+    Lo = opcases.Layout()
+    z = Lo.put(opcases._rn(rng, rows, classes))
+    lab = Lo.put(rng.integers(0, classes, rows).astype(np.int32))
+    loss, probs = Lo.out(1), Lo.out(rows * classes)
+    tmp = [Lo.out(rows * classes) for _ in range(8)]
+    big_rows = 4096
+    z2 = Lo.put(opcases._rn(rng, big_rows, 8))
+    lab2 = Lo.put(rng.integers(0, 8, big_rows).astype(np.int32))
+    loss2, probs2 = Lo.out(1), Lo.out(big_rows * 8)
+    arena, ro = Lo.done()
+    I = opcases._ins
+    prog = [I(Op.XENT_FWD, [z, lab, loss, probs], [rows, classes])]
+    src = probs
+    for t in tmp:                                         # a chain long enough to be graph-captured
+        prog.append(I(Op.SCALE, [src, t, F.f32_bits(1.5)], [rows * classes]))
+        src = t
+    prog = np.concatenate(prog)
+    ctx = Context(arena.size, ro)
+    ctx.write(0, arena)
+    pid = ctx.build(prog)
+    outs = []
+    for _ in range(3):                                    # direct run, capture, replay
+        ctx.run(pid, 0, len(prog))
+        outs.append(ctx.read(0, arena.size).copy())
+    ctx.execute(I(Op.XENT_FWD, [z2, lab2, loss2, probs2], [big_rows, 8]))    # needs a larger loss scratch
+    ctx.write(0, arena)
+    ctx.run(pid, 0, len(prog))
+    again = ctx.read(0, arena.size)
+    ctx.close()
+    np.testing.assert_array_equal(outs[0], outs[1])
+    np.testing.assert_array_equal(outs[0], outs[2])
+    np.testing.assert_array_equal(outs[0], again)
