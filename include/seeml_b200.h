@@ -187,6 +187,24 @@ int seeml_b200_grads_unpack(seeml_b200_ctx* ctx, const uint64_t* offsets,
 int seeml_b200_tree_sum(seeml_b200_ctx* ctx, void* sets_device, uint64_t floats_per_set,
                         uint64_t count, float scale);
 
+/* ------------------------------------------------------------ data-parallel exchange --
+ * No counterpart in the reference (single process). One communicator per GPU process (NCCL over
+ * NVLink, bound at run time). Rank 0 makes a 128-byte id with comm_unique_id and hands it to
+ * every rank by whatever channel the host has (a file, a socket, MPI, torch.distributed); every
+ * rank then calls comm_init. allgather enqueues on `stream`; comm_wait waits for the stream on
+ * the host while polling the communicator, and aborts it with an error if NCCL reports one or
+ * nothing completes within timeout_s (a rank that never posted), instead of hanging. */
+#define SEEML_B200_COMM_ID_BYTES 128
+typedef struct seeml_b200_comm seeml_b200_comm;
+int seeml_b200_comm_unique_id(void* id_out);
+int seeml_b200_comm_init(int device, const void* id, int rank, int world, seeml_b200_comm** out);
+void seeml_b200_comm_destroy(seeml_b200_comm* comm);
+int seeml_b200_comm_rank(const seeml_b200_comm* comm);
+int seeml_b200_comm_world(const seeml_b200_comm* comm);
+int seeml_b200_comm_allgather(seeml_b200_comm* comm, const void* send_device, void* recv_device,
+                              uint64_t floats, void* stream);
+int seeml_b200_comm_wait(seeml_b200_comm* comm, void* stream, double timeout_s);
+
 /* ------------------------------------------------------------------- datasets --
  * SDS corpora — runtime/feeder/dataset.h:43-152, dataset.cc:86-462. Host code;
  * serving order, shuffle and token label derivation are bit-exact. */
@@ -276,6 +294,24 @@ seeml_b200_ctx* seeml_b200_engine_ctx(seeml_b200_engine* e);
 uint64_t seeml_b200_engine_opt_begin(const seeml_b200_engine* e);
 /* Runs train instructions [begin, end) with the engine's current step scalars. */
 int seeml_b200_engine_run_train_range(seeml_b200_engine* e, uint64_t begin, uint64_t end);
+/* The K-chunk data-parallel step (no counterpart in the reference; its single-process step is
+ * update_engine.cc:736-771). A global step is `chunks_per_step` executions of the train stream
+ * up to the first optimiser instruction, each on its own batch of the plan's compiled size;
+ * rank r runs chunks [r K/world, (r+1) K/world). The per-chunk gradient sets and losses are
+ * summed in one fixed binary tree over the chunk index (local subtree, NCCL all-gather, the rest
+ * of the tree in rank order), scaled by 1/K, and every rank runs the optimiser instructions on
+ * identical bits: 1, 2, 4 and 8 GPUs give bit-identical parameters. chunks_per_step and world
+ * must be powers of two with world <= chunks_per_step; comm may be NULL when world == 1 and is
+ * borrowed otherwise. dp_step_host takes this rank's chunks back to back in HOST memory (copied
+ * through pinned staging on the copy stream, overlapped with the previous chunk's compute);
+ * dp_step_device takes them in DEVICE memory. Each call advances the engine's step; `loss`
+ * (nullable) receives the mean loss over all K chunks and makes the call synchronous. */
+int seeml_b200_engine_dp_configure(seeml_b200_engine* e, uint64_t chunks_per_step, int rank, int world,
+                                   seeml_b200_comm* comm);
+int seeml_b200_engine_dp_step_host(seeml_b200_engine* e, const void* inputs, const void* labels, float* loss);
+int seeml_b200_engine_dp_step_device(seeml_b200_engine* e, const void* inputs_device,
+                                     const void* labels_device, float* loss);
+uint64_t seeml_b200_engine_dp_local_chunks(const seeml_b200_engine* e);
 /* Kernels launched by the most recent train-program execution. */
 uint64_t seeml_b200_engine_last_launches(const seeml_b200_engine* e);
 /* StepTimings (update_engine.h:84-89), from CUDA events at the same two

@@ -79,6 +79,17 @@ SIGNATURES = {
     "seeml_b200_grads_pack": (INT, [vp, vp, vp, u64, vp]),
     "seeml_b200_grads_unpack": (INT, [vp, vp, vp, u64, vp]),
     "seeml_b200_tree_sum": (INT, [vp, vp, u64, u64, f32]),
+    "seeml_b200_comm_unique_id": (INT, [vp]),
+    "seeml_b200_comm_init": (INT, [INT, vp, INT, INT, C.POINTER(vp)]),
+    "seeml_b200_comm_destroy": (None, [vp]),
+    "seeml_b200_comm_rank": (INT, [vp]),
+    "seeml_b200_comm_world": (INT, [vp]),
+    "seeml_b200_comm_allgather": (INT, [vp, vp, vp, u64, vp]),
+    "seeml_b200_comm_wait": (INT, [vp, vp, C.c_double]),
+    "seeml_b200_engine_dp_configure": (INT, [vp, u64, INT, INT, vp]),
+    "seeml_b200_engine_dp_step_host": (INT, [vp, vp, vp, C.POINTER(f32)]),
+    "seeml_b200_engine_dp_step_device": (INT, [vp, vp, vp, C.POINTER(f32)]),
+    "seeml_b200_engine_dp_local_chunks": (u64, [vp]),
     "seeml_b200_dataset_load": (vp, [cp]),
     "seeml_b200_dataset_from_tokens": (vp, [vp, u64, u64]),
     "seeml_b200_dataset_from_memory": (vp, [vp, vp, u64, u64, u32, u64]),

@@ -33,7 +33,7 @@ GXX_FLAGS = ["-O2", "-std=c++23", "-fPIC", "-pthread", "-I" + INCLUDE, "-I" + CS
              "-I" + os.path.join(CUDA, "include"), "-Wall", "-Wextra", "-Wno-unused-parameter"]
 
 CU_SRCS = ["kernels_mem.cu", "kernels_gemm_simt.cu", "kernels_skinny.cu", "gemm_tc.cu", "backend.cu", "xent_noalloc.cu"]
-CC_SRCS = ["validate.cc", "dataset.cc", "engine.cc"]
+CC_SRCS = ["validate.cc", "dataset.cc", "engine.cc", "comm.cc"]
 
 
 def _stale(src, obj, deps):

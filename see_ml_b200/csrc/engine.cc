@@ -128,6 +128,21 @@ struct Loaded {
 
 }  // namespace
 
+// K-chunk data-parallel step (configured by seeml_b200_engine_dp_configure).
+struct DpState {
+  uint64_t K = 0, local = 0, fps = 0;           // chunks per step, chunks on this rank, floats per packed set
+  int rank = 0, world = 1;
+  seeml_b200_comm* comm = nullptr;              // borrowed; null when world == 1
+  float* sets = nullptr;                        // [local][fps]: one packed gradient set (+ loss) per chunk
+  float* gathered = nullptr;                    // [world][fps]
+  k::Span* spans = nullptr;                     // device span table: gradient operands, then the loss slot
+  uint64_t nspans = 0;
+  uint8_t* pin_in[2] = {nullptr, nullptr};
+  uint8_t* pin_lab[2] = {nullptr, nullptr};
+  uint64_t launches = 0;
+  double timeout_s = 120.0;
+};
+
 struct seeml_b200_engine {
   int device = 0;
   uint32_t mode = SEEML_B200_MODE_CONTRACT, gemm = SEEML_B200_GEMM_TF32X3;
@@ -141,9 +156,21 @@ struct seeml_b200_engine {
   double t_fwd = 0, t_bwd = 0, t_opt = 0;
   cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
   unsigned long long* counter_dev = nullptr;
+  DpState dp;
 };
 
 namespace {
+
+void free_dp(DpState& d) {
+  cudaFree(d.sets);
+  cudaFree(d.gathered);
+  cudaFree(d.spans);
+  for (int i = 0; i < 2; ++i) {
+    seeml_b200_pinned_free(d.pin_in[i]);
+    seeml_b200_pinned_free(d.pin_lab[i]);
+  }
+  d = DpState{};
+}
 
 void free_loaded(Loaded& L) {
   if (L.ctx) seeml_b200_ctx_destroy(L.ctx);
@@ -226,6 +253,7 @@ int initialize(seeml_b200_engine* e, const uint8_t* plan, uint64_t size, std::ve
   L.train_instrs = std::move(train);
   L.owned = std::move(owned);
   // commit: nothing below can fail
+  free_dp(e->dp);
   free_loaded(e->L);
   e->L = std::move(L);
   e->loaded = true;
@@ -442,6 +470,7 @@ seeml_b200_engine* seeml_b200_engine_create(int device, uint32_t mode, uint32_t 
 void seeml_b200_engine_destroy(seeml_b200_engine* e) {
   if (!e) return;
   cudaSetDevice(e->device);
+  free_dp(e->dp);
   free_loaded(e->L);
   for (auto& ev : e->ev) cudaEventDestroy(ev);
   cudaFree(e->counter_dev);
@@ -643,6 +672,160 @@ int seeml_b200_engine_train(seeml_b200_engine* e, seeml_b200_dataset* data, uint
   if (report) *report = rep;
   return 0;
 }
+
+// ---- K-chunk data-parallel step -------------------------------------------------------------
+// A global step is K executions ("chunks") of the train stream up to the first optimiser
+// instruction (update_engine.cc:249-261), each on its own batch; rank r of `world` runs chunks
+// [r K/world, (r+1) K/world). Every chunk's gradient operands (in[1] of the optimiser
+// instructions) and its loss are packed into one set; the sets are summed in ONE fixed binary
+// tree over the chunk index - the local subtree on this GPU, then an NCCL all-gather of the
+// world's partial sums and the rest of the tree in rank order - scaled by 1/K, unpacked into the
+// gradient slots, and every rank runs the optimiser instructions on identical bits. K and world
+// are powers of two, so 1, 2, 4 and 8 GPUs give bit-identical parameters.
+static bool pow2(uint64_t v) { return v && !(v & (v - 1)); }
+
+int seeml_b200_engine_dp_configure(seeml_b200_engine* e, uint64_t chunks_per_step, int rank, int world,
+                                   seeml_b200_comm* comm) {
+  if (!e || !e->loaded) return fail("UpdateEngine: no plan loaded");
+  if (!pow2(chunks_per_step) || world < 1 || !pow2((uint64_t)world) || (uint64_t)world > chunks_per_step)
+    return fail("UpdateEngine: chunks per step and world size must be powers of two with world <= chunks");
+  if (rank < 0 || rank >= world) return fail("UpdateEngine: rank out of range");
+  if (world > 1 && !comm) return fail("UpdateEngine: a communicator is required when world > 1");
+  if (cudaError_t ce = cudaSetDevice(e->device); ce != cudaSuccess) return cuda_fail(ce, "cudaSetDevice");
+  free_dp(e->dp);
+  DpState d;
+  d.K = chunks_per_step;
+  d.rank = rank;
+  d.world = world;
+  d.local = chunks_per_step / (uint64_t)world;
+  d.comm = world > 1 ? comm : nullptr;
+  if (const char* t = std::getenv("SEEML_B200_COMM_TIMEOUT_S")) d.timeout_s = std::atof(t);
+  const Loaded& L = e->L;
+  std::vector<k::Span> spans;
+  uint64_t at = 0;
+  for (const Instr& ins : L.train_instrs)
+    if (ins.opcode == kSgd || ins.opcode == kAdamW) {
+      spans.push_back({ref_off(ins.in[1]), ins.out[0], at});
+      at += ins.out[0];
+    }
+  spans.push_back({ref_off(L.h.loss_ref), 1, at});      // the chunk loss rides the set as one more span
+  d.fps = at + 1;
+  d.nspans = spans.size();
+  const uint64_t in_bytes = L.h.input_floats * 4, lab_bytes = L.h.label_kind == 0 ? 0 : L.h.label_bytes;
+  bool ok = cudaMalloc(&d.sets, d.local * d.fps * sizeof(float)) == cudaSuccess &&
+            cudaMalloc(&d.gathered, (uint64_t)world * d.fps * sizeof(float)) == cudaSuccess &&
+            cudaMalloc(&d.spans, spans.size() * sizeof(k::Span)) == cudaSuccess &&
+            cudaMemcpy(d.spans, spans.data(), spans.size() * sizeof(k::Span), cudaMemcpyHostToDevice) == cudaSuccess;
+  for (int i = 0; i < 2 && ok; ++i) {
+    d.pin_in[i] = static_cast<uint8_t*>(seeml_b200_pinned_alloc(in_bytes));
+    d.pin_lab[i] = static_cast<uint8_t*>(seeml_b200_pinned_alloc(lab_bytes ? lab_bytes : 4));
+    ok = d.pin_in[i] && d.pin_lab[i];
+  }
+  if (!ok) {
+    cudaGetLastError();
+    free_dp(d);
+    return fail("UpdateEngine: data-parallel buffers could not be allocated");
+  }
+  e->dp = d;
+  return 0;
+}
+
+namespace {
+
+int dp_chunk(seeml_b200_engine* e, uint64_t c) {      // stream up to the optimiser, then pack set c
+  Loaded& L = e->L;
+  DpState& d = e->dp;
+  const seeml_b200_scalars sc = scalars_of(e);
+  if (int r = seeml_b200_program_run(L.ctx, L.train, 0, L.opt_begin, &sc)) return r;
+  d.launches += seeml_b200_program_launches(L.ctx, L.train);
+  cudaStream_t st = static_cast<cudaStream_t>(seeml_b200_ctx_stream(L.ctx));
+  d.launches += k::pack_spans(static_cast<uint8_t*>(seeml_b200_ctx_arena(L.ctx)), d.spans, d.nspans, d.sets + c * d.fps,
+                              0, d.fps, st);
+  return 0;
+}
+
+int dp_finish(seeml_b200_engine* e, float* loss) {    // tree, exchange, optimiser
+  Loaded& L = e->L;
+  DpState& d = e->dp;
+  cudaStream_t st = static_cast<cudaStream_t>(seeml_b200_ctx_stream(L.ctx));
+  uint8_t* arena = static_cast<uint8_t*>(seeml_b200_ctx_arena(L.ctx));
+  float* total = d.sets;
+  const float inv_k = 1.0f / static_cast<float>(d.K);
+  if (d.world > 1) {
+    d.launches += k::tree_sum(d.sets, d.fps, d.local, 1.0f, st);
+    if (int r = seeml_b200_comm_allgather(d.comm, d.sets, d.gathered, d.fps, st)) return r;
+    d.launches += 1;
+    total = d.gathered;
+    d.launches += k::tree_sum(total, d.fps, (uint64_t)d.world, inv_k, st);
+  } else {
+    d.launches += k::tree_sum(total, d.fps, d.local, inv_k, st);
+  }
+  d.launches += k::pack_spans(arena, d.spans, d.nspans, total, 1, d.fps, st);
+  const seeml_b200_scalars sc = scalars_of(e);
+  if (int r = seeml_b200_program_run(L.ctx, L.train, L.opt_begin, L.train_instrs.size(), &sc)) return r;
+  d.launches += seeml_b200_program_launches(L.ctx, L.train);
+  e->merged = false;
+  e->last_launches = d.launches;
+  if (d.world > 1 && loss)                       // never block on a collective without a deadline
+    if (int r = seeml_b200_comm_wait(d.comm, st, d.timeout_s)) return r;
+  if (loss) return seeml_b200_read_f32(L.ctx, ref_off(L.h.loss_ref), loss);
+  return 0;
+}
+
+}  // namespace
+
+int seeml_b200_engine_dp_step_device(seeml_b200_engine* e, const void* inputs_device, const void* labels_device,
+                                     float* loss) {
+  if (!e || !e->loaded || e->dp.K == 0) return fail("UpdateEngine: data-parallel step is not configured");
+  if (!inputs_device) return fail("UpdateEngine: null argument");
+  Loaded& L = e->L;
+  DpState& d = e->dp;
+  const uint64_t in_bytes = L.h.input_floats * 4, lab_bytes = L.h.label_kind == 0 ? 0 : L.h.label_bytes;
+  ++e->step;
+  d.launches = 0;
+  for (uint64_t c = 0; c < d.local; ++c) {
+    if (int r = seeml_b200_d2d(L.ctx, ref_off(L.h.input_ref), static_cast<const uint8_t*>(inputs_device) + c * in_bytes,
+                               in_bytes))
+      return r;
+    if (lab_bytes && labels_device)
+      if (int r = seeml_b200_d2d(L.ctx, ref_off(L.h.label_ref),
+                                 static_cast<const uint8_t*>(labels_device) + c * lab_bytes, lab_bytes))
+        return r;
+    d.launches += 2;
+    if (int r = dp_chunk(e, c)) return r;
+  }
+  return dp_finish(e, loss);
+}
+
+int seeml_b200_engine_dp_step_host(seeml_b200_engine* e, const void* inputs, const void* labels, float* loss) {
+  if (!e || !e->loaded || e->dp.K == 0) return fail("UpdateEngine: data-parallel step is not configured");
+  if (!inputs) return fail("UpdateEngine: null argument");
+  Loaded& L = e->L;
+  DpState& d = e->dp;
+  const uint64_t in_bytes = L.h.input_floats * 4, lab_bytes = L.h.label_kind == 0 ? 0 : L.h.label_bytes;
+  const bool has_lab = lab_bytes && labels;
+  ++e->step;
+  d.launches = 0;
+  auto stage = [&](uint64_t c) -> int {           // pinned staging + H2D on the copy stream
+    const int s = (int)(c & 1);
+    if (int r = seeml_b200_stage_wait(L.ctx, s)) return r;      // the slot's previous copy has left the pinned buffer
+    std::memcpy(d.pin_in[s], static_cast<const uint8_t*>(inputs) + c * in_bytes, in_bytes);
+    if (has_lab) std::memcpy(d.pin_lab[s], static_cast<const uint8_t*>(labels) + c * lab_bytes, lab_bytes);
+    return seeml_b200_stage_h2d(L.ctx, s, d.pin_in[s], in_bytes, has_lab ? d.pin_lab[s] : nullptr, lab_bytes);
+  };
+  if (int r = stage(0)) return r;
+  for (uint64_t c = 0; c < d.local; ++c) {
+    const int s = (int)(c & 1);
+    if (int r = seeml_b200_stage_commit(L.ctx, s, ref_off(L.h.input_ref), ref_off(L.h.label_ref))) return r;
+    d.launches += 2;
+    if (int r = dp_chunk(e, c)) return r;
+    if (c + 1 < d.local)                          // the next chunk's copy overlaps this chunk's compute
+      if (int r = stage(c + 1)) return r;
+  }
+  return dp_finish(e, loss);
+}
+
+uint64_t seeml_b200_engine_dp_local_chunks(const seeml_b200_engine* e) { return e ? e->dp.local : 0; }
 
 // update_engine.cc:789-811 — the finiteness scan of the deltas runs on the device.
 int seeml_b200_engine_run_merge(seeml_b200_engine* e) {

@@ -23,7 +23,7 @@ import numpy as np
 
 from . import _lib as L
 from .engine import UpdateEngine
-from .formats import Op, parse_plan
+from .formats import Op
 
 
 def _is_pow2(n: int) -> bool:
@@ -55,119 +55,77 @@ def tree_sum_host(sets: np.ndarray) -> np.ndarray:
 
 
 class DataParallelTrainer:
-    """One rank of a data-parallel job. With world_size == 1 no process group is needed."""
+    """One rank of a data-parallel job: a thin caller of the C ABI's K-chunk step
+    (seeml_b200_engine_dp_configure / dp_step_host / dp_step_device). With world_size == 1
+    no communicator is needed. With more ranks the NCCL id made by rank 0 is handed round
+    through `group` (a torch.distributed process group, used for that one broadcast only)
+    or passed in as `comm_id` (128 bytes) by a host that has its own channel."""
 
     def __init__(self, plan: bytes, chunks_per_step: int, rank: int = 0, world_size: int = 1,
-                 device: int = 0, mode: int = 0, gemm: int = 0, group=None):
-        import torch
+                 device: int = 0, mode: int = 0, gemm: int = 0, group=None, comm_id: bytes | None = None):
         if not (_is_pow2(chunks_per_step) and _is_pow2(world_size) and world_size <= chunks_per_step):
             raise ValueError("chunks_per_step and world_size must be powers of two, world_size <= chunks")
-        self.torch = torch
-        self.K, self.rank, self.world = chunks_per_step, rank, world_size
+        lib = L.lib()
+        self.K, self.rank, self.world, self.device = chunks_per_step, rank, world_size, device
         self.local = chunks_per_step // world_size
-        self.group = group
         self.engine = UpdateEngine(device, mode, gemm)
         self.engine.load_from_memory(plan)
         self.h = self.engine.header
-        p = parse_plan(plan)
-        self.n_train = len(p.train)
-        self.opt_begin = self.engine.opt_begin()
-        self.offs, self.counts = gradient_spans(p.train)
-        self.fps = int(self.counts.sum()) + 1          # + the chunk loss
-        self.dev = torch.device("cuda", device)
         self.ctx = self.engine.ctx()
-        self.stream = torch.cuda.ExternalStream(L.lib().seeml_b200_ctx_stream(self.ctx), device=self.dev)
-        with torch.cuda.device(self.dev):
-            self.sets = torch.zeros((max(self.local, 1), self.fps), dtype=torch.float32, device=self.dev)
-            self.gathered = torch.zeros((world_size, self.fps), dtype=torch.float32, device=self.dev)
-        # the loss rides the packed set as one more span
-        self.pack_offs = np.concatenate([self.offs, np.array([self.h.loss_ref], np.uint64)])
-        self.pack_counts = np.concatenate([self.counts, np.array([1], np.uint64)])
-        self.step_index = 0
+        self.comm = C.c_void_p()
+        if world_size > 1:
+            if comm_id is None:
+                import torch
+                buf = torch.zeros(128, dtype=torch.uint8, device=torch.device("cuda", device))
+                if rank == 0:
+                    raw = (C.c_uint8 * 128)()
+                    L.check(lib.seeml_b200_comm_unique_id(raw))
+                    buf.copy_(torch.tensor(list(raw), dtype=torch.uint8))
+                torch.distributed.broadcast(buf, src=0, group=group)
+                comm_id = bytes(buf.cpu().tolist())
+            idbuf = (C.c_uint8 * 128).from_buffer_copy(comm_id)
+            L.check(lib.seeml_b200_comm_init(device, idbuf, rank, world_size, C.byref(self.comm)))
+        L.check(lib.seeml_b200_engine_dp_configure(self.engine.h, chunks_per_step, rank, world_size, self.comm))
         self.launches = 0
-        in_bytes = self.h.input_floats * 4
-        self._pin_in = [L.lib().seeml_b200_pinned_alloc(in_bytes) for _ in range(2)]
-        self._pin_lab = [L.lib().seeml_b200_pinned_alloc(max(self.h.label_bytes, 4)) for _ in range(2)]
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
-    # -- one global step -----------------------------------------------------------------
-    def _pack(self, local_chunk: int):
-        lib = L.lib()
-        dst = self.sets[local_chunk].data_ptr()
-        L.check(lib.seeml_b200_grads_pack(self.ctx, self.pack_offs.ctypes.data, self.pack_counts.ctypes.data,
-                                          len(self.pack_offs), C.c_void_p(dst)))
-
-    def _reduce_and_step(self):
-        lib, torch = L.lib(), self.torch
-        L.check(lib.seeml_b200_tree_sum(self.ctx, C.c_void_p(self.sets.data_ptr()), self.fps, self.local, 1.0))
-        if self.world > 1:
-            with torch.cuda.stream(self.stream):
-                torch.distributed.all_gather_into_tensor(self.gathered, self.sets[0], group=self.group)
-            total = self.gathered
-        else:
-            total = self.sets
-        L.check(lib.seeml_b200_tree_sum(self.ctx, C.c_void_p(total.data_ptr()), self.fps,
-                                        self.world if self.world > 1 else 1, 1.0 / self.K))
-        L.check(lib.seeml_b200_grads_unpack(self.ctx, self.pack_offs.ctypes.data, self.pack_counts.ctypes.data,
-                                            len(self.pack_offs), C.c_void_p(total.data_ptr())))
-        self.engine.run_train_range(self.opt_begin, self.n_train)
-        self.launches += self.engine.last_launches() + 4
+    @property
+    def stream(self):
+        """The compute stream as a torch stream (for CUDA-event timing by the caller)."""
+        import torch
+        return torch.cuda.ExternalStream(L.lib().seeml_b200_ctx_stream(self.ctx),
+                                         device=torch.device("cuda", self.device))
 
     def step(self, tokens: np.ndarray, labels: np.ndarray) -> float:
         """One global step from HOST buffers: `tokens` / `labels` hold this rank's `local`
-        chunks back to back ([local, batch] words each). Copies ride pinned staging
-        buffers and the copy stream; the mean loss over all K chunks is read back."""
-        lib = L.lib()
-        self.step_index += 1
-        self.engine.set_step(self.step_index)
-        self.launches = 0
-        in_b, lab_b = self.h.input_floats * 4, self.h.label_bytes
-        tok = np.ascontiguousarray(tokens).reshape(self.local, -1).view(np.uint8)
-        lab = np.ascontiguousarray(labels).reshape(self.local, -1).view(np.uint8)
-
-        def stage(c):
-            s = c & 1
-            C.memmove(self._pin_in[s], tok[c].ctypes.data, in_b)
-            C.memmove(self._pin_lab[s], lab[c].ctypes.data, lab_b)
-            L.check(lib.seeml_b200_stage_h2d(self.ctx, s, self._pin_in[s], in_b, self._pin_lab[s], lab_b))
-        stage(0)
-        for c in range(self.local):
-            s = c & 1
-            L.check(lib.seeml_b200_stage_commit(self.ctx, s, self.h.input_ref, self.h.label_ref))
-            L.check(lib.seeml_b200_stage_wait(self.ctx, s))
-            self.engine.run_train_range(0, self.opt_begin)
-            self.launches += self.engine.last_launches() + 2
-            if c + 1 < self.local:
-                stage(c + 1)            # next chunk's copy overlaps this chunk's compute
-            self._pack(c)
-        self._reduce_and_step()
-        self.h2d_bytes = self.local * (in_b + lab_b)
+        chunks back to back ([local, batch] words each). The mean loss over all K chunks is
+        read back."""
+        tok = np.ascontiguousarray(tokens)
+        lab = np.ascontiguousarray(labels)
+        loss = C.c_float()
+        L.check(L.lib().seeml_b200_engine_dp_step_host(self.engine.h, tok.ctypes.data_as(C.c_void_p),
+                                                       lab.ctypes.data_as(C.c_void_p), C.byref(loss)))
+        self.launches = self.engine.last_launches()
+        self.h2d_bytes = self.local * (self.h.input_floats * 4 + self.h.label_bytes)
         self.d2h_bytes = 4
-        return self.engine.loss_value()
+        return loss.value
 
     def step_resident(self, tokens_dev, labels_dev, read_loss: bool = False):
         """One global step with this rank's chunks already in HBM ([local, batch] i32 / f32
-        torch tensors): device-to-device moves into the I/O slots only."""
-        lib = L.lib()
-        self.step_index += 1
-        self.engine.set_step(self.step_index)
-        self.launches = 0
-        in_b, lab_b = self.h.input_floats * 4, self.h.label_bytes
-        for c in range(self.local):
-            L.check(lib.seeml_b200_d2d(self.ctx, self.h.input_ref, C.c_void_p(tokens_dev[c].data_ptr()), in_b))
-            L.check(lib.seeml_b200_d2d(self.ctx, self.h.label_ref, C.c_void_p(labels_dev[c].data_ptr()), lab_b))
-            self.engine.run_train_range(0, self.opt_begin)
-            self.launches += self.engine.last_launches() + 2
-            self._pack(c)
-        self._reduce_and_step()
-        return self.engine.loss_value() if read_loss else None
+        torch tensors, contiguous): device-to-device moves into the I/O slots only."""
+        loss = C.c_float()
+        L.check(L.lib().seeml_b200_engine_dp_step_device(self.engine.h, C.c_void_p(tokens_dev.data_ptr()),
+                                                         C.c_void_p(labels_dev.data_ptr()),
+                                                         C.byref(loss) if read_loss else None))
+        self.launches = self.engine.last_launches()
+        return loss.value if read_loss else None
 
     def persistent(self) -> np.ndarray:
         return self.engine.arena_read(0, self.h.persistent_size)
 
     def close(self):
-        for p in self._pin_in + self._pin_lab:
-            L.lib().seeml_b200_pinned_free(p)
-        self._pin_in, self._pin_lab = [], []
         self.engine.close()
+        if self.comm:
+            L.lib().seeml_b200_comm_destroy(self.comm)
+            self.comm = C.c_void_p()
