@@ -45,6 +45,9 @@ CONFIGS = {
 }
 
 
+GEMM_KINDS = {"tf32x3": 0, "f16x2": 1, "simt": 2, "tf32": 3}
+
+
 def build_model(cfg, seed=1):
     rng = np.random.default_rng(seed)
     if cfg["kind"] == "mlp":
@@ -159,16 +162,19 @@ def measured_peaks():
 
 # ------------------------------------------------------------------------------- reference arm
 def cpu_reference_sample(cfg, model, steps, warmup, threads):
-    """Times the reference's own CPU runtime (oracle/_ref) — or the C restatement when the
-    reference build is absent — on a bounded sample of the workload: one sequence (token
-    configs) or one compiled batch (MLP) per step."""
+    """Times the reference's own CPU runtime (oracle/_ref: UpdateEngine::ExecuteTrainOnce, its stock
+    path, built with its phase timers) - or the C restatement when the reference build is absent -
+    on a bounded sample of the workload: a plan compiled for one sequence (token configs) or one
+    compiled batch (MLP) of the same model. The reference pays forward + backward per row and the
+    optimiser once per global step, so the rate for the workload's global step is
+    global_rows / (fwd_bwd_seconds_per_row * global_rows + optimiser_seconds)."""
     from oracle import pyoracle as O
     rows = cfg["seq"] if cfg["kind"] != "mlp" else cfg["rows"]
+    global_rows = (cfg["rows"] if cfg["kind"] == "mlp" else cfg["seqs"] * cfg["seq"]) * cfg["chunks"]
     hasher = lambda b, o: int(O.port().orc_plan_self_hash(np.frombuffer(b, np.uint8).ctypes.data, len(b), o))
     blob, _ = build_plan(cfg, model, rows, hasher)
     inp, lab = synth_batches(cfg, rows, 1, seed=5)
     h = F.PlanHeader.unpack(blob)
-    times = []
     if O.have_ref():
         kind = "reference"
         O.ref().ref_set_threads(threads)
@@ -176,25 +182,39 @@ def cpu_reference_sample(cfg, model, steps, warmup, threads):
         arena = e.arena()
         arena[h.input_ref:h.input_ref + inp[0].nbytes] = inp[0].view(np.uint8)
         arena[h.label_ref:h.label_ref + lab[0].nbytes] = lab[0].view(np.uint8)
-        for i in range(warmup + steps):
-            t0 = time.perf_counter()
+        for _ in range(warmup):
             e.execute_train_once()
-            times.append(time.perf_counter() - t0)
+        s0 = e.step_timings()
+        for _ in range(steps):
+            e.execute_train_once()
+        s1 = e.step_timings()
+        n = max(s1[0] - s0[0], 1)
+        t_fb = ((s1[1] - s0[1]) + (s1[2] - s0[2])) / n
+        t_opt = (s1[3] - s0[3]) / n
     else:
         kind, threads = "port", 1
         plan = F.parse_plan(blob)
+        opt_begin = int(np.nonzero(np.isin(plan.train["opcode"], (17, 18, 28)))[0][0])
         arena = np.zeros(F.align_up(h.arena_size), np.uint8)
         arena[:h.persist_init_size] = plan.persist_init
         arena[h.input_ref:h.input_ref + inp[0].nbytes] = inp[0].view(np.uint8)
         arena[h.label_ref:h.label_ref + lab[0].nbytes] = lab[0].view(np.uint8)
+        t_fb = t_opt = 0.0
         for i in range(warmup + steps):
             t0 = time.perf_counter()
-            O.execute("port", plan.train, arena, np.asarray(plan.rodata), lr=h.lr, step=i + 1)
-            times.append(time.perf_counter() - t0)
-    t = float(np.mean(times[warmup:])) if steps else float("nan")
-    return dict(value=rows / t, unit="tokens/s", cores=threads, kind=kind,
-                sample=f"{steps} step(s) of {rows} rows (one sequence of the workload's model), "
-                       f"{warmup} warm-up"), t * 1e3
+            O.execute("port", plan.train[:opt_begin], arena, np.asarray(plan.rodata), lr=h.lr, step=i + 1)
+            t1 = time.perf_counter()
+            O.execute("port", plan.train[opt_begin:], arena, np.asarray(plan.rodata), lr=h.lr, step=i + 1)
+            t2 = time.perf_counter()
+            if i >= warmup:
+                t_fb += (t1 - t0) / max(steps, 1)
+                t_opt += (t2 - t1) / max(steps, 1)
+    t_global = t_fb * (global_rows / rows) + t_opt
+    return dict(value=global_rows / t_global, unit="tokens/s", cores=threads, kind=kind,
+                sample=f"{steps} timed execution(s) of a {rows}-row plan of the workload's model after {warmup} warm-up: "
+                       f"forward+backward {t_fb * 1e3:.1f} ms per {rows} rows, optimiser {t_opt * 1e3:.2f} ms; rate for the "
+                       f"{global_rows}-row global step = rows / (fwd_bwd per row * rows + optimiser)",
+                rows_timed=rows, fwd_bwd_ms=t_fb * 1e3, opt_ms=t_opt * 1e3), t_global * 1e3
 
 
 def run_reference(args, cfg):
@@ -203,11 +223,14 @@ def run_reference(args, cfg):
         return
     model = build_model(cfg)
     threads = os.cpu_count() or 1
-    base, ms = cpu_reference_sample(cfg, model, args.steps, min(args.warmup, 1), threads)
+    base, ms = cpu_reference_sample(cfg, model, args.steps, args.warmup, threads)
+    config = workload_config(args, cfg)
+    config["reference_rows_timed_per_execution"] = base["rows_timed"]
+    config["sampled_rate"] = True
     line = {"metric": "train tokens/sec per update step", "value": base["value"], "unit": "tokens/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": ms,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "impl": "reference", "config": workload_config(args, cfg),
+            "data": "synthetic", "impl": "reference", "config": config,
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0}}
@@ -254,7 +277,7 @@ def run_ours(args, cfg):
     rows = cfg["rows"] if cfg["kind"] == "mlp" else cfg["seqs"] * cfg["seq"]
     K = max(cfg["chunks"], world)
     blob, _ = build_plan(cfg, model, rows, hasher)
-    gemm = {"tf32x3": 0, "bf16": 1, "simt": 2, "tf32": 3}[args.gemm]
+    gemm = GEMM_KINDS[args.gemm]
     tr = DataParallelTrainer(blob, K, rank, world, local_rank, mode=1 if args.fused else 0, gemm=gemm,
                              group=group)
     local = tr.local
@@ -313,9 +336,10 @@ def run_ours(args, cfg):
     # ---- arm B: end to end through the public API from host buffers --------------------------
     e2e = None
     if not args.no_e2e:
-        e2e_steps = max(1, min(args.steps, 3))
+        e2e_steps = max(1, args.steps)
         hb = [batches_for(100 + s) for s in range(e2e_steps + 1)]
-        tr.step(*hb[0])
+        for _ in range(min(args.warmup, 2)):
+            tr.step(*hb[0])
         barrier()
         with torch.cuda.stream(tr.stream):
             ev0.record()
@@ -360,7 +384,7 @@ def run_ours(args, cfg):
             torch.cuda.synchronize()
             t_ms = ev0.elapsed_time(ev1) / reps
             ach = fl / (t_ms * 1e-3) / 1e12
-            issue = {"tf32x3": 3, "tf32": 1}.get(args.gemm)
+            issue = {"tf32x3": 3, "f16x2": 3, "tf32": 1}.get(args.gemm)
             roof = {"bound": "tensor", "kernel": f"gemm_tc_kernel M={m} N={n} K={k} ({args.gemm})",
                     "achieved": ach, "peak": tf_burst, "unit": "TFLOP/s", "frac": ach / tf_burst,
                     "peak_source": f"bf16 dense burst, {src}", "traffic": profiled_traffic(m, n, k),
@@ -377,6 +401,7 @@ def run_ours(args, cfg):
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": {"tf32x3": "f32 (3xTF32 tensor-core split, f32 accumulate)",
+                          "f16x2": "f32 (two-term fp16 split of scaled operands, three products, f32 accumulate)",
                           "simt": "f32", "tf32": "tf32"}[args.gemm],
                 "data": "synthetic", "config": workload_config(args, cfg),
                 "mode": "fused" if args.fused else "contract",
@@ -396,7 +421,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c4", choices=sorted(CONFIGS))
-    ap.add_argument("--gemm", default="tf32x3", choices=["tf32x3", "simt", "tf32"])
+    ap.add_argument("--gemm", default="tf32x3", choices=sorted(GEMM_KINDS))
     ap.add_argument("--fused", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--chunks", type=int, default=0, help="override chunks per step (profiling aid)")

@@ -515,7 +515,10 @@ void seeml_b200_ctx_destroy(seeml_b200_ctx* c) {
   for (auto& p : c->programs)
     if (p) {
       for (auto& g : p->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
-      for (auto& fs : p->steps) cudaFree(fs.bt);
+      for (auto& fs : p->steps) {
+        cudaFree(fs.bt);
+        cudaFree(fs.descs);
+      }
       cudaFree(p->side);
     }
   gemm_tensor_core_release(c);
@@ -613,7 +616,9 @@ int seeml_b200_program_run(seeml_b200_ctx* c, int id, uint64_t begin, uint64_t e
   Exec x{c};
   x.launches = 1;
   int failed = 0;
+  c->exec_unit += 2;
   for (uint64_t i = begin; i < end && !failed;) {
+    ++c->exec_unit;
     const int32_t si = p.step_at.empty() ? -1 : p.step_at[i];
     if (si >= 0 && i + p.steps[si].count <= end) {
       const int fr = run_fused(x, p, p.steps[si]);

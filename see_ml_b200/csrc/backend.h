@@ -84,7 +84,8 @@ const float* gemm_tc_transposed_weight(seeml_b200_ctx* c, uint64_t rodata_off, u
 
 // A group of consecutive instructions executed by fewer, fused kernels (FUSED mode).
 struct FusedStep {
-  enum Kind { kLoraFwd = 1, kLoraBwd = 2, kDgradAdd = 3, kAttnDs = 4, kSwigluFwd = 5, kSwigluBwd = 6 } kind;
+  enum Kind { kLoraFwd = 1, kLoraBwd = 2, kDgradAdd = 3, kAttnDs = 4, kSwigluFwd = 5, kSwigluBwd = 6,
+              kRmsBwdAdd = 7, kXent = 8, kAdamWMulti = 9 } kind;
   uint32_t first = 0, count = 0;
   uint32_t idx[8] = {0, 0, 0, 0, 0, 0, 0, 0};   // instruction indices of the group's members by role
   float alpha = 1.0f;
@@ -92,6 +93,10 @@ struct FusedStep {
   bool da_last = false;                         // dA after the dgrad GEMM (slot reuse, see backend_fuse.inc)
   bool via_temp = false;                        // result lands in a dead slot first, then moves
   bool via_side = false;                        // result lands in the program's side buffer first, then moves
+  bool residual = false;                        // kLoraFwd: the residual add that follows rides the GEMM's addend
+  bool skip = false;                            // kSwigluBwd: ds is dead; kXent: probs is dead
+  seeml_b200::k::AdamwDesc* descs = nullptr;    // kAdamWMulti: device descriptor table
+  uint32_t ndesc = 0, blocks = 0;
 };
 
 struct Program {
@@ -136,6 +141,9 @@ struct seeml_b200_ctx {
   uint32_t gemm_kind = SEEML_B200_GEMM_TF32X3;
   bool timing = false, timed_valid = false;
   bool use_graphs = true;          // SEEML_B200_GRAPHS=0 turns graph replay off
+  // serial number of the instruction / fused group being enqueued: consecutive units of one run
+  // differ by one, separate runs by more (kernels use it to tell what may have changed in between)
+  uint64_t exec_unit = 0;
   seeml_b200::DevScalars* scalars_dev = nullptr;
   double* loss_scratch = nullptr;
   uint64_t loss_scratch_doubles = 0;

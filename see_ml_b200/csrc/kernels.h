@@ -41,8 +41,9 @@ int layernorm_bwd(const float* dy, const float* x, const float* g, const float* 
                   const float* rstd, float* dx, size_t rows, size_t cols, cudaStream_t st);
 int rmsnorm_fwd(const float* x, const float* g, float* y, float* rstd, size_t rows, size_t cols,
                 cudaStream_t st);
+// addend (nullable): dx = addend + gradient (the residual sum that follows in the stream)
 int rmsnorm_bwd(const float* dy, const float* x, const float* g, const float* rstd, float* dx,
-                size_t rows, size_t cols, cudaStream_t st);
+                size_t rows, size_t cols, cudaStream_t st, const float* addend = nullptr);
 
 // ---- rotary embedding (attention.cc:39-92). table = [S][d/2] (cos,sin) pairs
 // computed on the host with the reference's float recurrence. ----------------------
@@ -83,6 +84,17 @@ int count_correct(const float* probs, const int32_t* labels, size_t real, size_t
 int count_nonfinite(const float* x, size_t n, unsigned long long* counter, cudaStream_t st);
 
 // ---- data-parallel gradient plumbing ---------------------------------------------------
+// ---- groups of consecutive instructions run as one kernel (FUSED mode); n % 4 == 0 and
+// 16-byte aligned operands are the caller's job ----------------------------------------------
+int swiglu_fwd(const float* g, const float* u, float* s, float* m, size_t n, cudaStream_t st);
+int swiglu_bwd(const float* dm, const float* u, const float* s, const float* g, float* ds, float* du, float* dg,
+               size_t n, cudaStream_t st);
+// loss, (probs when not null) and dlogits = (seed / N) (p - onehot) in one pass; scratch as xent_fwd
+int xent_fused(const float* logits, const int32_t* labels, float* loss, float* probs, float* dlogits, float seed,
+               size_t N, size_t C, double* scratch, cudaStream_t st);
+struct AdamwDesc { float* p; const float* g; float* m; float* v; uint64_t n; uint32_t first_block; uint32_t pad; };
+int adamw_multi(const AdamwDesc* descs_dev, int ndesc, unsigned total_blocks, const DevScalars* sc, cudaStream_t st);
+
 struct Span { uint64_t arena_off; uint64_t count; uint64_t packed_off; };
 int pack_spans(const uint8_t* arena, const Span* spans_dev, size_t nspans, float* packed,
                int unpack, size_t total, cudaStream_t st);

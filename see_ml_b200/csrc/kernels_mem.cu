@@ -299,8 +299,11 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_fwd_kernel(
 }
 template <int TPR>
 __global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(
-    const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ g,
-    const float* __restrict__ rstd, float* __restrict__ dx, size_t rows, size_t cols, int vec) {
+    const float* dy, const float* x, const float* __restrict__ g,
+    const float* __restrict__ rstd, float* dx, const float* addend, size_t rows, size_t cols, int vec) {
+  // addend (nullable): dx = addend + (the gradient), for the residual sum that follows in the
+  // stream; dx may then alias dy, x or addend exactly (every element is read by the thread that
+  // later writes it, within one row)
   ROW_SETUP(TPR)
   const float inv_d = 1.0f / (float)cols;
   for (size_t r = row0; r < rows; r += rstride) {
@@ -331,11 +334,17 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(
         o.y = rs * (d4.y * g4.y - x4.y * rs * rs * mgx);
         o.z = rs * (d4.z * g4.z - x4.z * rs * rs * mgx);
         o.w = rs * (d4.w * g4.w - x4.w * rs * rs * mgx);
+        if (addend != nullptr) {
+          const float4 a4 = reinterpret_cast<const float4*>(addend + r * cols)[c];
+          o.x = a4.x + o.x; o.y = a4.y + o.y; o.z = a4.z + o.z; o.w = a4.w + o.w;
+        }
         reinterpret_cast<float4*>(dx + r * cols)[c] = o;
       }
     } else {
-      for (size_t c = lane; c < cols; c += TPR)
-        dx[r * cols + c] = rs * (dyr[c] * g[c] - xr[c] * rs * rs * mgx);
+      for (size_t c = lane; c < cols; c += TPR) {
+        const float o = rs * (dyr[c] * g[c] - xr[c] * rs * rs * mgx);
+        dx[r * cols + c] = addend != nullptr ? addend[r * cols + c] + o : o;
+      }
     }
   }
 }
@@ -671,6 +680,100 @@ __global__ void __launch_bounds__(kThreads) adamw_kernel(float* __restrict__ p,
   }
 }
 
+// ---- fused groups of FUSED mode (same expressions and roundings as the kernels they replace) ----
+// SwiGLU forward: s = silu(g), m = s * u in one pass.
+__global__ void __launch_bounds__(kThreads) swiglu_fwd_kernel(const float4* g, const float4* u, float4* s,
+                                                              float4* m, size_t n4) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 gv = g[i], uv = u[i];
+    float4 sv, mv;
+    sv.x = silu_e(gv.x); sv.y = silu_e(gv.y); sv.z = silu_e(gv.z); sv.w = silu_e(gv.w);
+    mv.x = sv.x * uv.x; mv.y = sv.y * uv.y; mv.z = sv.z * uv.z; mv.w = sv.w * uv.w;
+    s[i] = sv;
+    m[i] = mv;
+  }
+}
+// SwiGLU backward: ds = dm * u, du = dm * s, dg = silu'(g) ds in one pass. Outputs may alias
+// inputs exactly (du over u, dg over s): a thread reads element i of every input before it
+// writes element i of any output. ds is written only when something later reads it.
+__global__ void __launch_bounds__(kThreads) swiglu_bwd_kernel(const float4* dm, const float4* u, const float4* s,
+                                                              const float4* g, float4* ds, float4* du,
+                                                              float4* dg, size_t n4) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 d = dm[i], uv = u[i], sv = s[i], gv = g[i];
+    float4 a, b, c;
+    a.x = d.x * uv.x; a.y = d.y * uv.y; a.z = d.z * uv.z; a.w = d.w * uv.w;
+    b.x = d.x * sv.x; b.y = d.y * sv.y; b.z = d.z * sv.z; b.w = d.w * sv.w;
+    c.x = silu_d(a.x, gv.x); c.y = silu_d(a.y, gv.y); c.z = silu_d(a.z, gv.z); c.w = silu_d(a.w, gv.w);
+    if (ds != nullptr) ds[i] = a;
+    du[i] = b;
+    dg[i] = c;
+  }
+}
+// Softmax cross-entropy forward and backward in one pass over the logits: the row's
+// exponentials are parked in the gradient row, the loss term is taken from them, then the row
+// becomes dlogits = scale * p (label entry - scale). probs is written only when something later
+// reads it. d may be the logits row itself. Values equal the two-kernel path bit for bit.
+template <int TPR>
+__global__ void __launch_bounds__(kThreads) xent_fused_rows_kernel(
+    const float* logits, const int32_t* __restrict__ labels, float* probs, float* d,
+    double* __restrict__ terms, size_t N, size_t C, float scale) {
+  __shared__ double smd[8];
+  __shared__ float smf[8];
+  const int lane = TPR == 32 ? (threadIdx.x & 31) : threadIdx.x;
+  const size_t rpb = kThreads / TPR;
+  const size_t row0 = blockIdx.x * rpb + (TPR == 32 ? (threadIdx.x >> 5) : 0);
+  for (size_t n = row0; n < N; n += (size_t)gridDim.x * rpb) {
+    const float* z = logits + n * C;
+    float* e = d + n * C;
+    float mx = -INFINITY;
+    for (size_t c = lane; c < C; c += TPR) mx = fmaxf(mx, z[c]);
+    mx = row_max<TPR>(mx, smf);
+    double sum = 0.0;
+    for (size_t c = lane; c < C; c += TPR) {
+      const float ev = expf(z[c] - mx);
+      e[c] = ev;
+      sum += ev;
+    }
+    sum = row_sum<TPR>(sum, smd);
+    const float inv = 1.0f / (float)sum;
+    if (TPR != 32) __syncthreads();
+    else __syncwarp();
+    const uint32_t lab = (uint32_t)labels[n];
+    if (lane == 0) {
+      const float pl = lab < C ? e[lab] * inv : __int_as_float(0x7fc00000);
+      const double safe = isnan(pl) ? (double)pl : (double)fmaxf(pl, 1e-12f);
+      terms[n] = -log(safe);
+    }
+    if (TPR != 32) __syncthreads();
+    else __syncwarp();
+    for (size_t c = lane; c < C; c += TPR) {
+      const float p = e[c] * inv;
+      if (probs != nullptr) probs[n * C + c] = p;
+      float v = scale * p;
+      if (c == lab) v -= scale;
+      e[c] = v;
+    }
+  }
+}
+// Every AdamW instruction of a run in one launch: block b serves 1024 elements of the tensor whose
+// block range holds b. Element arithmetic is adamw_one, as in adamw_kernel.
+__global__ void __launch_bounds__(kThreads) adamw_multi_kernel(const AdamwDesc* __restrict__ descs, int ndesc,
+                                                               const DevScalars* __restrict__ scp) {
+  const DevScalars s = *scp;
+  int lo = 0, hi = ndesc;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (descs[mid].first_block <= blockIdx.x) lo = mid; else hi = mid;
+  }
+  const AdamwDesc t = descs[lo];
+  const size_t base = (size_t)(blockIdx.x - t.first_block) * 1024;
+  for (int q = 0; q < 4; ++q) {
+    const size_t i = base + q * 256 + threadIdx.x;
+    if (i < t.n) adamw_one(t.p[i], t.g[i], t.m[i], t.v[i], s);
+  }
+}
+
 // ---- gate metrics ---------------------------------------------------------------------------
 // Exact argmax accuracy: the first column holding the row maximum wins, as the
 // reference's strict '>' scan does. One warp per row; integer atomics only.
@@ -820,10 +923,11 @@ int rmsnorm_fwd(const float* x, const float* g, float* y, float* rstd, size_t ro
   return 1;
 }
 int rmsnorm_bwd(const float* dy, const float* x, const float* g, const float* rstd, float* dx,
-                size_t rows, size_t cols, cudaStream_t st) {
+                size_t rows, size_t cols, cudaStream_t st, const float* addend) {
   if (rows == 0) return 0;
-  const int vec = cols % 4 == 0 && aligned16(x) && aligned16(g) && aligned16(dy) && aligned16(dx);
-  ROW_LAUNCH(rmsnorm_bwd_kernel, rows, cols, dy, x, g, rstd, dx, rows, cols, vec);
+  const int vec = cols % 4 == 0 && aligned16(x) && aligned16(g) && aligned16(dy) && aligned16(dx) &&
+                  (addend == nullptr || aligned16(addend));
+  ROW_LAUNCH(rmsnorm_bwd_kernel, rows, cols, dy, x, g, rstd, dx, addend, rows, cols, vec);
   return 1;
 }
 int rope(const float* x, float* y, const float2* table, size_t B, size_t S, size_t H, size_t d,
@@ -941,6 +1045,39 @@ int adamw(float* p, const float* g, float* m, float* v, size_t n, const DevScala
   if (n == 0) return 0;
   const int vec = aligned16(p) && aligned16(g) && aligned16(m) && aligned16(v);
   adamw_kernel<<<grid_for(n / (vec ? 4 : 1) + 1, kThreads), kThreads, 0, st>>>(p, g, m, v, n, sc, vec);
+  return 1;
+}
+int swiglu_fwd(const float* g, const float* u, float* s, float* m, size_t n, cudaStream_t st) {
+  if (n == 0) return 0;
+  swiglu_fwd_kernel<<<grid_for(n / 4, kThreads), kThreads, 0, st>>>(
+      reinterpret_cast<const float4*>(g), reinterpret_cast<const float4*>(u), reinterpret_cast<float4*>(s),
+      reinterpret_cast<float4*>(m), n / 4);
+  return 1;
+}
+int swiglu_bwd(const float* dm, const float* u, const float* s, const float* g, float* ds, float* du, float* dg,
+               size_t n, cudaStream_t st) {
+  if (n == 0) return 0;
+  swiglu_bwd_kernel<<<grid_for(n / 4, kThreads), kThreads, 0, st>>>(
+      reinterpret_cast<const float4*>(dm), reinterpret_cast<const float4*>(u), reinterpret_cast<const float4*>(s),
+      reinterpret_cast<const float4*>(g), reinterpret_cast<float4*>(ds), reinterpret_cast<float4*>(du),
+      reinterpret_cast<float4*>(dg), n / 4);
+  return 1;
+}
+int xent_fused(const float* logits, const int32_t* labels, float* loss, float* probs, float* dlogits, float seed,
+               size_t N, size_t C, double* scratch, cudaStream_t st) {
+  if (N == 0) return 0;
+  const float scale = seed / (float)N;
+  if (C <= 1024)
+    xent_fused_rows_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(logits, labels, probs, dlogits,
+                                                                                   scratch, N, C, scale);
+  else
+    xent_fused_rows_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(logits, labels, probs, dlogits,
+                                                                             scratch, N, C, scale);
+  return 1 + finish_loss(scratch, N, chunk_grain(N, row_grain(C, 4096)), (double)N, loss, st);
+}
+int adamw_multi(const AdamwDesc* descs_dev, int ndesc, unsigned total_blocks, const DevScalars* sc, cudaStream_t st) {
+  if (ndesc == 0 || total_blocks == 0) return 0;
+  adamw_multi_kernel<<<total_blocks, kThreads, 0, st>>>(descs_dev, ndesc, sc);
   return 1;
 }
 int count_correct(const float* probs, const int32_t* labels, size_t real, size_t C,

@@ -158,3 +158,48 @@ def test_lora_matmul_sweep_forward_dgrad_wgrad(kn):
             ctx.close()
         if r >= 16:
             assert launches[MODE_FUSED] < launches[MODE_CONTRACT], "the LoRA groups were not fused"
+
+
+def test_elementwise_fused_groups_are_bit_identical_to_the_instruction_path():
+    """SwiGLU forward / backward, softmax-xent forward + seed + backward, an RMSNorm backward with
+    the residual sum behind it and a run of AdamW instructions: in fused mode each group is one
+    kernel, and every value a later instruction could read equals the per-instruction path's bits
+    (the skipped intermediates are overwritten afterwards, as liveness demands)."""
+    from see_ml_b200.engine import Context, MODE_CONTRACT, MODE_FUSED
+    from see_ml_b200.formats import Op
+    rng = np.random.default_rng(77)
+    T, Fd, D, V = 96, 64, 48, 200
+    n = T * Fd
+    Lo = opcases.Layout()
+    g, u, dm = Lo.put(opcases._rn(rng, n)), Lo.put(opcases._rn(rng, n)), Lo.put(opcases._rn(rng, n))
+    s, m, ds = Lo.out(n), Lo.out(n), Lo.out(n)
+    logits, labels = Lo.put(opcases._rn(rng, T, V, scale=2.0)), Lo.put(rng.integers(0, V, T).astype(np.int32))
+    loss, probs, seed = Lo.out(1), Lo.out(T * V), Lo.out(1)
+    dy, xin, rstd_src = Lo.put(opcases._rn(rng, T, D)), Lo.put(opcases._rn(rng, T, D)), Lo.put(np.abs(opcases._rn(rng, T)) + 0.5)
+    gamma = Lo.put(opcases._rn(rng, D), ro=True)
+    skip, dx, xsum = Lo.put(opcases._rn(rng, T, D)), Lo.out(T * D), Lo.out(T * D)
+    params = [(Lo.put(opcases._rn(rng, k)), Lo.put(opcases._rn(rng, k, scale=0.1)), Lo.put(np.zeros(k, np.float32)),
+               Lo.put(np.zeros(k, np.float32)), k) for k in (1024, 37, 4096, 5000)]
+    arena, ro = Lo.done()
+    I = opcases._ins
+    prog = [I(Op.SILU_FWD, [g, s], [n]), I(Op.MUL, [s, u, m], [n]),
+            # backward of the product: du lands on u, dg on s, as the compiler's planner does it
+            I(Op.MUL, [dm, u, ds], [n]), I(Op.MUL, [dm, s, u], [n]), I(Op.SILU_BWD, [ds, g, s], [n]),
+            I(Op.FILL, [ds, F.f32_bits(0.0)], [n]),                                  # ds's slot is reused: it was dead
+            I(Op.XENT_FWD, [logits, labels, loss, probs], [T, V]), I(Op.FILL, [seed, F.f32_bits(1.0)], [1]),
+            I(Op.XENT_BWD, [probs, labels, seed, logits], [T, V]),
+            I(Op.FILL, [probs, F.f32_bits(0.0)], [T * V]),                           # probs dead as well
+            I(Op.RMSNORM_BWD, [dy, xin, gamma, dx], [rstd_src, F.pack32(T, D)]), I(Op.ADD, [skip, dx, xsum], [T * D]),
+            I(Op.FILL, [dx, F.f32_bits(0.0)], [T * D])]
+    prog += [I(Op.ADAMW, [p_, g_, m_, v_], [k]) for p_, g_, m_, v_, k in params]
+    prog = np.concatenate(prog)
+    outs = {}
+    for mode in (MODE_CONTRACT, MODE_FUSED):
+        ctx = Context(arena.size, ro)
+        ctx.write(0, arena)
+        pid = ctx.build(prog, mode=mode)
+        ctx.run(pid, 0, len(prog), step=3)
+        outs[mode] = (ctx.read(0, arena.size), ctx.launches(pid))
+        ctx.close()
+    np.testing.assert_array_equal(outs[MODE_FUSED][0], outs[MODE_CONTRACT][0])
+    assert outs[MODE_FUSED][1] <= outs[MODE_CONTRACT][1] - 8, outs[MODE_FUSED][1:] + outs[MODE_CONTRACT][1:]
