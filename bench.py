@@ -250,6 +250,249 @@ def workload_config(args, cfg):
     return d
 
 
+
+# ------------------------------------------------------------------------ HBM-bound kernel rooflines
+def hbm_rooflines(lib, dev, rows, d, ffn, vocab, rank, hbm_peak, src):
+    """Achieved bandwidth of the memory-bound kernels at the workload's shapes: algorithmic bytes
+    (each operand read once, each output written once) over the CUDA-event time of one launch on the
+    stream it runs on, L2 flushed (a 256 MB write) between launches."""
+    import torch
+    from see_ml_b200.engine import Context
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import opcases
+    Op = F.Op
+    rng = np.random.default_rng(3)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = []
+
+    def timed(name, build, bytes_):
+        Lo = opcases.Layout()
+        prog = build(Lo)
+        arena, ro = Lo.done()
+        ctx = Context(arena.size, ro, device=dev.index)
+        ctx.write(0, arena)
+        pid = ctx.build(prog, mode=1)
+        st = torch.cuda.ExternalStream(lib.seeml_b200_ctx_stream(ctx.h), device=dev)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ts = []
+        for it in range(6):
+            with torch.cuda.stream(st):
+                flush.fill_(it & 1)
+                ev0.record()
+                ctx.run(pid, 0, len(prog), sync=False)
+                ev1.record()
+            torch.cuda.synchronize()
+            if it:
+                ts.append(ev0.elapsed_time(ev1))
+        ctx.close()
+        ms = float(np.median(ts))
+        gbs = bytes_ / (ms * 1e-3) / 1e9
+        out.append({"kernel": name, "bound": "hbm", "algorithmic_bytes": int(bytes_), "ms_per_launch": ms, "achieved": gbs,
+                    "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak, "peak_source": f"copy bandwidth, {src}"})
+
+    I = opcases._ins
+    rn = lambda *sh: rng.standard_normal(sh, dtype=np.float32)
+    n = rows * ffn
+    timed(f"swiglu forward (silu + mul) [{rows}x{ffn}]",
+          lambda L: np.concatenate([I(Op.SILU_FWD, [L.put(rn(n)), (s_ := L.out(n))], [n]), I(Op.MUL, [s_, L.put(rn(n)), L.out(n)], [n])]),
+          4 * 4 * n)
+    n2 = rows * d
+    timed(f"add [{rows}x{d}]", lambda L: I(Op.ADD, [L.put(rn(n2)), L.put(rn(n2)), L.out(n2)], [n2]), 12 * n2)
+
+    def rms(L):
+        dy, x, g, rs = L.put(rn(n2)), L.put(rn(n2)), L.put(rn(d), ro=True), L.put(np.abs(rn(rows)) + 0.5)
+        return I(Op.RMSNORM_BWD, [dy, x, g, L.out(n2)], [rs, F.pack32(rows, d)])
+    timed(f"rmsnorm backward [{rows}x{d}]", rms, 12 * n2)
+    xr = min(rows, 4096)
+
+    def xent(L):
+        z, lab = L.put(rn(xr, vocab)), L.put(rng.integers(0, vocab, xr).astype(np.int32))
+        loss, probs, seed = L.out(1), L.out(xr * vocab), L.out(1)
+        return np.concatenate([I(Op.XENT_FWD, [z, lab, loss, probs], [xr, vocab]), I(Op.FILL, [seed, F.f32_bits(1.0)], [1]),
+                               I(Op.XENT_BWD, [probs, lab, seed, z], [xr, vocab]), I(Op.FILL, [probs, 0], [4])])
+    timed(f"softmax-xent forward + backward [{xr}x{vocab}]", xent, 8 * xr * vocab)
+
+    def adam(L):
+        sizes = [d * rank, rank * d, d * rank, rank * ffn, ffn * rank, rank * d] * 24
+        return np.concatenate([I(Op.ADAMW, [L.put(rn(k)), L.put(rn(k)), L.put(np.zeros(k, np.float32)), L.put(np.zeros(k, np.float32))], [k])
+                               for k in sizes])
+    nparam = sum([d * rank, rank * d, d * rank, rank * ffn, ffn * rank, rank * d]) * 24
+    timed(f"adamw, 144 adapter tensors in one launch ({nparam} parameters)", adam, 28 * nparam)
+    return out
+
+
+# ------------------------------------------------------------------------------- C5: MatMul / LoRA sweep
+def run_sweep(args):
+    """BASELINE configs[4]: Y = X.W + (alpha/r)(X.A).B with its backward (dX, dA, dB), fp32 in / out,
+    M in {2048, 16384, 131072}, (K, N) in {(1024,1024), (1024,2816), (2816,1024), (4096,4096)}, r in {8,16,64},
+    entries ~N(0,1). Each shape runs as the instruction sequences the compiler emits, in fused mode; the
+    forward group and the backward group (dgrad + both weight gradients) are timed separately."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+    from see_ml_b200 import _lib as L
+    from see_ml_b200.engine import Context, MODE_FUSED
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import opcases
+    lib = L.lib()
+    Op = F.Op
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    hbm, tf_burst, tf_sust, src = measured_peaks()
+    gemm = GEMM_KINDS[args.gemm]
+    I = opcases._ins
+    rows_out, tot_fl, tot_ms = [], 0.0, 0.0
+    Ms = [int(m) for m in args.sweep_m.split(",")]
+    gen = torch.Generator(device=dev)
+    for M in Ms:
+        for (K, N) in [(1024, 1024), (1024, 2816), (2816, 1024), (4096, 4096)]:
+            for r in (8, 16, 64):
+                alpha = 2.0 * r
+                Lo, cur = {}, 0
+                def slot(name, count):
+                    nonlocal cur
+                    Lo[name] = cur
+                    cur = F.align_up(cur + 4 * count, 256)
+                for nm, cnt in (("x", M * K), ("a", K * r), ("b", r * N), ("g", M * N), ("c", M * N), ("t", M * r), ("u", M * N),
+                                ("s", M * N), ("y", M * N), ("ds", M * N), ("dt", M * r), ("dB", r * N), ("dx1", M * K),
+                                ("dA", K * r), ("dx2", M * K), ("dX", M * K)):
+                    slot(nm, cnt)
+                gen.manual_seed(M * 31 + K * 7 + N + r)
+                W = torch.randn(K * N, generator=gen, device=dev, dtype=torch.float32)
+                ctx = Context(cur + 4096, W.cpu().numpy().view(np.uint8), device=dev.index, gemm=gemm)
+                del W
+                base = lib.seeml_b200_ctx_arena(ctx.h)
+                for nm, cnt in (("x", M * K), ("a", K * r), ("b", r * N), ("g", M * N)):
+                    v = torch.randn(cnt, generator=gen, device=dev, dtype=torch.float32)
+                    L.check(lib.seeml_b200_d2d(ctx.h, Lo[nm], v.data_ptr(), 4 * cnt))
+                    L.check(lib.seeml_b200_sync(ctx.h))
+                    del v
+                w = F.RODATA_BIT | 0
+                sc = F.f32_bits(alpha / r)
+                o = Lo
+                fwd = np.concatenate([I(Op.GEMM_NN, [o["x"], w, o["c"]], [M, N, K]), I(Op.GEMM_NN, [o["x"], o["a"], o["t"]], [M, r, K]),
+                                      I(Op.GEMM_NN, [o["t"], o["b"], o["u"]], [M, N, r]), I(Op.SCALE, [o["u"], o["s"], sc], [M * N]),
+                                      I(Op.ADD, [o["c"], o["s"], o["y"]], [M * N])])
+                bwd = np.concatenate([I(Op.SCALE, [o["g"], o["ds"], sc], [M * N]), I(Op.GEMM_NT, [o["ds"], o["b"], o["dt"]], [M, r, N]),
+                                      I(Op.GEMM_TN, [o["t"], o["ds"], o["dB"]], [r, N, M]), I(Op.GEMM_NT, [o["dt"], o["a"], o["dx1"]], [M, K, r]),
+                                      I(Op.GEMM_TN, [o["x"], o["dt"], o["dA"]], [K, r, M]), I(Op.GEMM_NT, [o["g"], w, o["dx2"]], [M, K, N]),
+                                      I(Op.ADD, [o["dx1"], o["dx2"], o["dX"]], [M * K])])
+                prog = np.concatenate([fwd, bwd])
+                pid = ctx.build(prog, mode=MODE_FUSED)
+                st = torch.cuda.ExternalStream(lib.seeml_b200_ctx_stream(ctx.h), device=dev)
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+                tf_, tb_ = [], []
+                for it in range(4):
+                    with torch.cuda.stream(st):
+                        ev[0].record()
+                        ctx.run(pid, 0, len(fwd), sync=False)
+                        ev[1].record()
+                        ctx.run(pid, len(fwd), len(prog), sync=False)
+                        ev[2].record()
+                    torch.cuda.synchronize()
+                    if it:
+                        tf_.append(ev[0].elapsed_time(ev[1]))
+                        tb_.append(ev[1].elapsed_time(ev[2]))
+                ctx.close()
+                f_ms, b_ms = float(np.median(tf_)), float(np.median(tb_))
+                f_fl = 2.0 * M * K * N + 2.0 * M * K * r + 2.0 * M * r * N
+                b_fl = 2.0 * M * K * N + 2.0 * (2.0 * M * N * r + 2.0 * M * K * r)
+                rows_out.append({"M": M, "K": K, "N": N, "r": r, "forward_ms": f_ms, "backward_ms": b_ms,
+                                 "forward_tflops": f_fl / (f_ms * 1e-3) / 1e12, "backward_tflops": b_fl / (b_ms * 1e-3) / 1e12,
+                                 "forward_frac": f_fl / (f_ms * 1e-3) / 1e12 / tf_burst,
+                                 "backward_frac": b_fl / (b_ms * 1e-3) / 1e12 / tf_burst})
+                tot_fl += f_fl + b_fl
+                tot_ms += f_ms + b_ms
+    cpu = None
+    if not args.no_cpu_baseline:
+        from oracle import pyoracle as O
+        kind = "reference" if O.have_ref() else "port"
+        if kind == "reference":
+            O.ref().ref_set_threads(os.cpu_count() or 1)
+        rng = np.random.default_rng(0)
+        cl = []
+        Mc = 2048
+        for (K, N) in [(1024, 1024), (1024, 2816), (2816, 1024), (4096, 4096)]:
+            Lo = opcases.Layout()
+            x, g_ = Lo.put(rng.standard_normal((Mc, K), dtype=np.float32)), Lo.put(rng.standard_normal((Mc, N), dtype=np.float32))
+            wv = Lo.put(rng.standard_normal((K, N), dtype=np.float32), ro=True)
+            y, dx = Lo.out(Mc * N), Lo.out(Mc * K)
+            arena, ro = Lo.done()
+            res = {}
+            for nm, ins in (("GemmNN", I(Op.GEMM_NN, [x, wv, y], [Mc, N, K])), ("GemmNT", I(Op.GEMM_NT, [g_, wv, dx], [Mc, K, N]))):
+                t0 = time.perf_counter()
+                O.execute("ref" if kind == "reference" else "port", ins, arena, ro)
+                res[nm] = 2.0 * Mc * K * N / (time.perf_counter() - t0) / 1e9
+            cl.append({"M": Mc, "K": K, "N": N, **{k + "_gflops": v for k, v in res.items()}})
+        cpu = {"value": float(np.mean([c["GemmNN_gflops"] for c in cl])) / 1e3, "unit": "TFLOP/s", "cores": os.cpu_count() if kind == "reference" else 1,
+               "kind": kind, "sample": "kernels::GemmNN / GemmNT, one call per (K, N) at M = 2048 (the rate does not depend on M)", "shapes": cl}
+    value = tot_fl / (tot_ms * 1e-3) / 1e12
+    best = max(rows_out, key=lambda r_: r_["forward_tflops"])
+    line = {"metric": "MatMul/LoRA sweep: algorithmic TFLOP/s, forward + backward over all shapes", "value": value, "unit": "TFLOP/s",
+            "n_gpus": 1, "steps": 3, "warmup": 1, "ms_per_step": tot_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": args.gemm, "data": "synthetic", "config": {"workload": "c5", "M": Ms, "mode": "fused", "l2": "operands exceed L2 except at M = 2048"},
+            "roofline": {"bound": "tensor", "kernel": f"best forward shape M={best['M']} K={best['K']} N={best['N']} r={best['r']}",
+                         "achieved": best["forward_tflops"], "peak": tf_burst, "unit": "TFLOP/s", "frac": best["forward_frac"],
+                         "peak_source": f"bf16 dense burst, {src}", "traffic": None},
+            "sweep": rows_out, "cpu_baseline": cpu, "gpu_launches": None, "e2e": None}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------- seeml-bench shaped report (C1-C3)
+def run_seeml_bench(args):
+    """The reference's benchmark report (tool/seeml_bench.cc:289-334) for this backend: per fixture the plan
+    statistics, load time, and - by steps regression between two run lengths, medians over repeats - the
+    per-step time, rows/s, GEMM GFLOP/s and the forward / backward / optimiser split of StepTimings."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from see_ml_b200 import _lib as L
+    from see_ml_b200.engine import Dataset, UpdateEngine
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import cfgcases
+    lib = L.lib()
+    hasher = lambda b, o: int(lib.seeml_b200_plan_self_hash(np.frombuffer(b, np.uint8).ctypes.data, len(b), o))
+    lo, hi, repeats = args.steps_lo, args.steps_hi, 3
+    fixtures = {}
+    for name in args.seeml_bench.split(","):
+        cfg, model, spec = cfgcases.model_and_spec(name)
+        t0 = time.perf_counter()
+        blob, _ = PS.synthesize(model, spec, hasher=hasher)
+        compile_ms = (time.perf_counter() - t0) * 1e3
+        plan = F.parse_plan(blob)
+        h = plan.header
+        flops, _ = plan_work(blob)
+        e = UpdateEngine(int(os.environ.get("LOCAL_RANK", "0")), 1, GEMM_KINDS[args.gemm])
+        t0 = time.perf_counter()
+        e.load_from_memory(blob)
+        load_ms = (time.perf_counter() - t0) * 1e3
+        x, y = cfgcases.corpus(name)
+        ds = Dataset.from_memory(x, y) if y is not None else Dataset.from_tokens(x)
+        e.train(ds, 4)
+        e.enable_step_timing(True)
+        e.reset_step_timings()
+        slopes, life = [], []
+        for _ in range(repeats):
+            t0 = time.perf_counter(); e.train(ds, lo); w_lo = (time.perf_counter() - t0) * 1e3
+            t0 = time.perf_counter(); e.train(ds, hi); w_hi = (time.perf_counter() - t0) * 1e3
+            slopes.append((w_hi - w_lo) / (hi - lo))
+            life.append(w_lo - slopes[-1] * lo)
+        steps, fwd, bwd, opt = e.step_timings()
+        step_ms = float(np.median(slopes))
+        t0 = time.perf_counter(); e.run_merge(); merge_ms = (time.perf_counter() - t0) * 1e3
+        fixtures[name] = {"kind": cfg["kind"], "batch_rows": int(h.batch), "seq": int(h.seq_len), "plan_bytes": len(blob),
+                          "arena_bytes": int(h.arena_size), "persistent_bytes": int(h.persistent_size), "rodata_bytes": int(h.rodata_size),
+                          "train_instructions": int(h.train_instr_count), "gemm_flops_per_step": int(flops),
+                          "compile_ms": round(compile_ms, 2), "load_ms": round(load_ms, 3),
+                          "threads": {"gpu": {"step_ms": round(step_ms, 3), "lifecycle_ms": round(float(np.median(life)), 2),
+                                              "rows_per_s": round(1000.0 * h.batch / step_ms), "gemm_gflops": round(flops / (step_ms * 1e6), 1),
+                                              "fwd_ms": round(1e3 * fwd / max(steps, 1), 3), "bwd_ms": round(1e3 * bwd / max(steps, 1), 3),
+                                              "opt_ms": round(1e3 * opt / max(steps, 1), 3)}},
+                          "merge_ms": round(merge_ms, 3)}
+        e.close()
+    print(json.dumps({"seeml_version": "seeml_b200", "schema": 1,
+                      "config": {"steps_lo": lo, "steps_hi": hi, "repeats": repeats, "threads": "gpu"}, "fixtures": fixtures}), flush=True)
+
+
 # ------------------------------------------------------------------------------------ our arm
 def run_ours(args, cfg):
     import torch
@@ -394,6 +637,9 @@ def run_ours(args, cfg):
                             "products per step (tf32 runs at half the bf16 rate), so 1/6 of the bf16 "
                             "peak is the ceiling of this column for tf32x3"}
             ctx.close()
+        hbm_lines = None
+        if not args.no_e2e and cfg["kind"] == "llama":
+            hbm_lines = hbm_rooflines(lib, dev, min(rows, 16384), cfg["d"], cfg["ffn"], cfg["vocab"], cfg["rank"], hbm, src)
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             cpu, _ = cpu_reference_sample(cfg, model, 1, 0, os.cpu_count() or 1)
@@ -407,7 +653,7 @@ def run_ours(args, cfg):
                 "mode": "fused" if args.fused else "contract",
                 "gemm_tflops_algorithmic": flops * K / (ms_step * 1e-3) / 1e12,
                 "loss": loss_a, "params_sha256_16": params_digest, "e2e": e2e, "gpu_launches": int(launches),
-                "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
+                "clocks": clocks, "roofline": roof, "rooflines_hbm": hbm_lines, "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)
     tr.close()
     if world > 1:
@@ -420,13 +666,21 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="c4", choices=sorted(CONFIGS))
-    ap.add_argument("--gemm", default="tf32x3", choices=sorted(GEMM_KINDS))
+    ap.add_argument("--config", default="c4", choices=sorted(CONFIGS) + ["c5"])
+    ap.add_argument("--sweep-m", default="2048,16384,131072", help="row counts of the c5 sweep")
+    ap.add_argument("--seeml-bench", default="", help="comma-separated fixtures (c1,c2,c3): print the seeml-bench shaped report")
+    ap.add_argument("--steps-lo", type=int, default=20)
+    ap.add_argument("--steps-hi", type=int, default=80)
+    ap.add_argument("--gemm", default="f16x2", choices=sorted(GEMM_KINDS))
     ap.add_argument("--fused", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--chunks", type=int, default=0, help="override chunks per step (profiling aid)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (profiling aid)")
     args = ap.parse_args()
+    if args.seeml_bench:
+        return run_seeml_bench(args)
+    if args.config == "c5":
+        return run_sweep(args)
     cfg = dict(CONFIGS[args.config])
     if args.chunks:
         cfg["chunks"] = args.chunks

@@ -13,7 +13,7 @@
 // memory: arena() is replaced by ArenaRead / ArenaWrite (explicit copies), and the engine is
 // created on the device named by SEEML_B200_DEVICE (default 0) in the execution mode named by
 // SEEML_B200_MODE ("fused", the default, or "contract") with the GEMM arithmetic named by
-// SEEML_B200_GEMM ("tf32x3" default, "f16x2", "tf32", "simt").
+// SEEML_B200_GEMM ("f16x2" default, "tf32x3", "tf32", "simt").
 #ifndef SEEML_COMPAT_RUNTIME_ENGINE_UPDATE_ENGINE_H_
 #define SEEML_COMPAT_RUNTIME_ENGINE_UPDATE_ENGINE_H_
 
@@ -202,7 +202,7 @@ class UpdateEngine {
     if (e_) return {};
     const char* dev = std::getenv("SEEML_B200_DEVICE");
     e_ = seeml_b200_engine_create(dev ? std::atoi(dev) : 0, EnvChoice("SEEML_B200_MODE", {"contract", "fused"}, 1),
-                                  EnvChoice("SEEML_B200_GEMM", {"tf32x3", "f16x2", "simt", "tf32"}, 0));
+                                  EnvChoice("SEEML_B200_GEMM", {"tf32x3", "f16x2", "simt", "tf32"}, 1));
     if (!e_) return std::unexpected(Err());
     return {};
   }

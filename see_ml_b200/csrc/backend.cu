@@ -28,6 +28,17 @@ int cuda_fail(cudaError_t e, const char* what) {
     if (e_ != cudaSuccess) return cuda_fail(e_, what);     \
   } while (0)
 
+// Captured range graphs hold the addresses of the context's scratch buffers: whenever one of
+// those buffers is replaced, every graph of the context is dropped (its range is captured again
+// on a later run).
+void drop_graphs(seeml_b200_ctx* c) {
+  for (auto& p : c->programs)
+    if (p) {
+      for (auto& g : p->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+      p->graphs.clear();
+    }
+}
+
 namespace {
 
 inline float bits_f32(uint64_t w) {
@@ -92,17 +103,6 @@ int ensure_rope(seeml_b200_ctx* c, uint64_t S, uint64_t dh, float base) {
   CU(cudaMemcpy(dev, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice), "rope table copy");
   c->rope[key] = dev;
   return 0;
-}
-
-// Captured range graphs hold the addresses of the context's scratch buffers: whenever one of
-// those buffers is replaced, every graph of the context is dropped (its range is captured again
-// on a later run).
-void drop_graphs(seeml_b200_ctx* c) {
-  for (auto& p : c->programs)
-    if (p) {
-      for (auto& g : p->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
-      p->graphs.clear();
-    }
 }
 
 int ensure_scratch(seeml_b200_ctx* c, uint64_t loss_doubles, uint64_t ws_floats) {

@@ -36,6 +36,8 @@ uint64_t plan_self_hash(const uint8_t* p, uint64_t n, uint64_t hash_off);
 }  // namespace seeml_b200
 struct seeml_b200_ctx;
 namespace seeml_b200 {
+// Destroys every captured range graph of the context (they are captured again on later runs).
+void drop_graphs(seeml_b200_ctx* c);
 int gemm_tensor_core(seeml_b200_ctx* c, const Instr& ins, int* launches);
 int gemm_tensor_core_prepare(seeml_b200_ctx* c, const Instr& ins);
 void gemm_tensor_core_release(seeml_b200_ctx* c);

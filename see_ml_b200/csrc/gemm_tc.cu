@@ -1285,6 +1285,331 @@ gemm_tc_pair_f16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_c
   if (warp == 1) tmem_dealloc2(tmem_base, 512);
 }
 
+
+// ------------------------------------- CTA-pair GEMM, fp16 split, operands pre-split (F16X2)
+// The arithmetic of gemm_tc_pair_f16_kernel with the conversion taken out of the GEMM: every
+// A operand is cut into its fp16 hi / lo terms once, by split_rows_f16_kernel (one pass over
+// the tensor: row maximum, power-of-two row scale, convert), instead of once per N tile inside
+// the GEMM; B comes from the frozen weight's copies as before. Every operand tile is then a
+// plain TMA load of fp16 (64 elements = one 128-byte swizzle row per k-block), the worker warps
+// only collect accumulation chunks and store, and three 64 KiB stages are all load buffers.
+// Scales are per ROW of A (exact powers of two, undone when a chunk is collected - the thread
+// that collects a row owns it), which also removes the dependence of a row's accuracy on the
+// largest magnitude anywhere else in the tensor.
+// Pair protocol: the even CTA's MMAs read both CTAs' shared memory, so the odd CTA's idle MMA
+// warp relays its "stage loaded" phases to the even CTA with one remote arrive per stage.
+constexpr int kF16pKB = 64;                       // fp16 elements per k-block: one 128-byte row
+constexpr int kF16pStages = 3;
+constexpr int kF16pTile = BM * kF16pKB * 2;       // 16 KiB: 128 rows x 64 fp16
+struct PairF16pSmem {
+  static constexpr int kAHi = 0, kALo = kF16pTile, kBHi = 2 * kF16pTile, kBLo = 3 * kF16pTile;
+  static constexpr int kStage = 4 * kF16pTile;    // 64 KiB
+  static constexpr int kTotal = kF16pStages * kStage + 256 + 1024;
+};
+struct F16pParams {
+  int M, N, K, K2;
+  const float* bias;
+  const float* addend;
+  int act;
+  float alpha;
+  int eb_pre;                  // scale exponent of the frozen B copies
+  const float* inv_a;          // [M]: 2^-e of each row of A (main pair)
+  const float* inv_a2;         // [M]: the same for the tail's A2
+  const uint32_t* absmax;      // slot 3: max|x| of the tail's B2 (its copies hold B2 * 2^e)
+  int n_tiles, total_tiles;
+  int* err;
+};
+
+__global__ void __launch_bounds__(kThreadsV2, 1)
+gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
+                         const __grid_constant__ CUtensorMap mapA2hi, const __grid_constant__ CUtensorMap mapA2lo,
+                         const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo,
+                         const __grid_constant__ CUtensorMap mapB2hi, const __grid_constant__ CUtensorMap mapB2lo,
+                         const __grid_constant__ CUtensorMap mapC, F16pParams p) {
+  using S = PairF16pSmem;
+  constexpr int STAGES = kF16pStages, BN = 256, KB = kF16pKB, CH = 2;   // CH k-blocks (128 elements of K) per chunk
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + STAGES * S::kStage;
+  auto bar_full = [&](int s) { return bars + 8u * s; };
+  auto bar_peer = [&](int s) { return bars + 8u * (STAGES + s); };        // even CTA: the odd CTA's stage has landed
+  auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+  auto bar_acc_full = [&](int b) { return bars + 8u * (3 * STAGES + b); };
+  auto bar_acc_empty = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
+  const uint32_t bar_epi = bars + 8u * (3 * STAGES + 4);
+  const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 5);
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (3 * STAGES + 5));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cid = (int)(blockIdx.x >> 1), ncl = (int)(gridDim.x >> 1);
+  auto tile_of = [&](int t, int& m0, int& n0) {
+    n0 = (t % p.n_tiles) * BN;
+    m0 = (2 * (t / p.n_tiles) + (int)rank) * BM;
+  };
+  const int nkb1 = (p.K + KB - 1) / KB;
+  const int nkb = nkb1 + (p.K2 + KB - 1) / KB;
+  const int nmain = (nkb1 + CH - 1) / CH;
+  const int nchunks = nmain + (nkb - nkb1 + CH - 1) / CH;
+  auto chunk_pos = [&](int kb, int& c, int& j, bool& last) {
+    if (kb < nkb1) { c = kb / CH; j = kb % CH; last = j == CH - 1 || kb == nkb1 - 1; }
+    else { const int q = kb - nkb1; c = nmain + q / CH; j = q % CH; last = j == CH - 1 || kb == nkb - 1; }
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_peer(s), 1);
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), 2 * kWorkers / 32);
+    }
+    mbar_init(bar_epi, kWorkers / 32);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ---- TMA producer: four fp16 tiles per stage ------------------------------------------------
+    if (lane == 0) {
+      int it = 0, ti = 0, pend = -1, epi_stage = -1;
+      bool ok = true;
+      for (int tl = cid; tl < p.total_tiles && ok; tl += ncl, ++ti) {
+        int m0, n0;
+        tile_of(tl, m0, n0);
+        const int nb = n0 + (int)rank * 128;
+        for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
+          const int s = it % STAGES, r = it / STAGES;
+          if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 51);
+          if (ok && pend >= 0 && s == epi_stage) {
+            ok = mbar_wait(bar_epi, pend & 1, p.err, 58);
+            pend = -1;
+          }
+          if (!ok) break;
+          const uint32_t stg = base + s * S::kStage;
+          mbar_expect_tx(bar_full(s), 4 * kF16pTile);
+          if (kb < nkb1) {
+            tma_load_2d(stg + S::kAHi, &mapAhi, bar_full(s), kb * KB, m0);
+            tma_load_2d(stg + S::kALo, &mapAlo, bar_full(s), kb * KB, m0);
+            tma_load_2d(stg + S::kBHi, &mapBhi, bar_full(s), kb * KB, nb);
+            tma_load_2d(stg + S::kBLo, &mapBlo, bar_full(s), kb * KB, nb);
+          } else {
+            tma_load_2d(stg + S::kAHi, &mapA2hi, bar_full(s), (kb - nkb1) * KB, m0);
+            tma_load_2d(stg + S::kALo, &mapA2lo, bar_full(s), (kb - nkb1) * KB, m0);
+            tma_load_2d(stg + S::kBHi, &mapB2hi, bar_full(s), (kb - nkb1) * KB, nb);
+            tma_load_2d(stg + S::kBLo, &mapB2lo, bar_full(s), (kb - nkb1) * KB, nb);
+          }
+        }
+        if (ok && pend >= 0) {
+          ok = mbar_wait(bar_epi, pend & 1, p.err, 58);
+          pend = -1;
+        }
+        pend = ti;
+        epi_stage = (it - 1) % STAGES;
+      }
+      if (!ok) {
+        for (int kb = (it > STAGES ? it - STAGES : 0); kb < it; ++kb)
+          mbar_wait(bar_full(kb % STAGES), (kb / STAGES) & 1, p.err, 55);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 1) {
+      // ---- odd CTA: relay "this CTA's stage has landed" to the even CTA ------------------------
+      bool ok = true;
+      int it = 0;
+      for (int tl = cid; tl < p.total_tiles && ok; tl += ncl)
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          ok = mbar_wait(bar_full(it % STAGES), (it / STAGES) & 1, p.err, 57);
+          if (!ok) break;
+          mbar_arrive_remote(bar_peer(it % STAGES), 0);
+        }
+    } else if (lane == 0) {
+      // ---- even CTA: MMA issuer ---------------------------------------------------------------
+      constexpr uint32_t idesc = idesc_f16(256, BN);
+      bool ok = true;
+      int it = 0, ci = 0;
+      for (int tl = cid; tl < p.total_tiles && ok; tl += ncl)
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = it % STAGES, r = it / STAGES;
+        const int buf = ci & 1;
+        int c, j;
+        bool last;
+        chunk_pos(kb, c, j, last);
+        if (j == 0 && ci >= 2) {
+          ok = mbar_wait(bar_acc_empty(buf), ((ci >> 1) - 1) & 1, p.err, 56);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        ok = mbar_wait(bar_full(s), r & 1, p.err, 52) && mbar_wait(bar_peer(s), r & 1, p.err, 59);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        const uint32_t stg = base + s * S::kStage;
+#pragma unroll
+        for (int kk = 0; kk < KB / 16; ++kk) {
+          const uint64_t da = smem_desc_sw128(stg + S::kAHi + kk * 32), dal = smem_desc_sw128(stg + S::kALo + kk * 32);
+          const uint64_t db = smem_desc_sw128(stg + S::kBHi + kk * 32), dbl = smem_desc_sw128(stg + S::kBLo + kk * 32);
+          mma_f16_pair(tmem_d, da, db, idesc, (j | kk) != 0);
+          mma_f16_pair(tmem_d, dal, db, idesc, 1);
+          mma_f16_pair(tmem_d, da, dbl, idesc, 1);
+        }
+        mma_commit_pair(bar_empty(s));
+        if (last) {
+          mma_commit_pair(bar_acc_full(buf));
+          ++ci;
+        }
+      }
+    }
+  } else {
+    // ---- worker warps (both CTAs): collect finished chunks, epilogue ----------------------------
+    const int q = warp & 3, half = (warp - 2) >> 2, row0 = q * 32;
+    constexpr int NH = BN / 2, LD = 32;
+    const float inv_b = pow2i(-p.eb_pre), inv_b2 = pow2i(-f16_scale_exp(p.absmax[3]));
+    float acc[NH];
+    bool ok = true;
+    int cg = 0, tiles_done = 0;
+    for (int tl = cid; tl < p.total_tiles && ok; tl += ncl, ++tiles_done) {
+      int m0, n0;
+      tile_of(tl, m0, n0);
+      const int m = m0 + row0 + lane;
+      const float cs_main = (m < p.M ? p.inv_a[m] : 1.0f) * inv_b;
+      const float cs_tail = (p.K2 && m < p.M ? p.inv_a2[m] : 1.0f) * inv_b2;
+#pragma unroll
+      for (int j = 0; j < NH; ++j) acc[j] = 0.0f;
+      for (int ci = 0; ci < nchunks && ok; ++ci, ++cg) {
+        const int buf = cg & 1;
+        ok = mbar_wait(bar_acc_full(buf), (cg >> 1) & 1, p.err, 54);
+        if (!ok) break;
+        tc_fence_after();
+        const float cs = ci < nmain ? cs_main : cs_tail;
+#pragma unroll
+        for (int c = 0; c < NH / LD; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + buf * BN + half * NH + c * LD, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]) * cs;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(bar_acc_empty(buf), 0);
+      }
+      if (!ok) break;
+      // the stage of the tile's last k-block is the one the producer refills last: store staging
+      const int it_last = (tiles_done + 1) * nkb - 1;
+      const uint32_t box = (uint32_t)((it_last % STAGES) * S::kStage + (warp - 2) * 4096);
+      if (m0 + row0 < p.M) {
+        bool stored = false;
+#pragma unroll
+        for (int c = 0; c < NH / LD; ++c) {
+          const int ncol = n0 + half * NH + c * LD;
+          if (ncol < p.N) {
+            uint8_t* stage_ptr = base_ptr + box;
+            if (stored) {
+              if (lane == 0) tma_store_wait_read();
+              __syncwarp();
+            }
+            stored = true;
+            uint32_t r[32];
+#pragma unroll
+            for (int j = 0; j < LD; ++j) r[j] = __float_as_uint(p.alpha * acc[c * LD + j]);
+            if (p.addend != nullptr && m < p.M) {
+              const float* arow = p.addend + (size_t)m * p.N + ncol;
+#pragma unroll
+              for (int j4 = 0; j4 < LD / 4; ++j4) {
+                if (ncol + 4 * j4 < p.N) {
+                  const float4 d = *reinterpret_cast<const float4*>(arow + 4 * j4);
+                  r[4 * j4 + 0] = __float_as_uint(d.x + __uint_as_float(r[4 * j4 + 0]));
+                  r[4 * j4 + 1] = __float_as_uint(d.y + __uint_as_float(r[4 * j4 + 1]));
+                  r[4 * j4 + 2] = __float_as_uint(d.z + __uint_as_float(r[4 * j4 + 2]));
+                  r[4 * j4 + 3] = __float_as_uint(d.w + __uint_as_float(r[4 * j4 + 3]));
+                }
+              }
+            }
+            if (p.bias != nullptr || p.act != 0) {
+#pragma unroll
+              for (int j = 0; j < LD; ++j) {
+                float v = __uint_as_float(r[j]);
+                if (p.bias != nullptr && ncol + j < p.N) v = v + p.bias[ncol + j];
+                r[j] = __float_as_uint(epi_act(p.act, v));
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < LD / 4; ++j) {
+              uint4 v = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+              *reinterpret_cast<uint4*>(stage_ptr + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&mapC, base + box, ncol, m0 + row0);
+              tma_store_commit();
+            }
+          }
+        }
+      }
+      if (lane == 0) {
+        tma_store_wait_read();
+        mbar_arrive(bar_epi);
+      }
+      __syncwarp();
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) tmem_dealloc2(tmem_base, 512);
+}
+
+// One pass over a row-major f32 tensor [M, K]: each row's largest magnitude picks its power-of-two
+// scale 2^e (max * 2^e in [2^13, 2^14)), the row is cut into fp16 hi = fp16(x 2^e) and
+// lo = fp16(x 2^e - hi), and 2^-e goes to inv[row]. One warp per row; the second sweep over the
+// row comes from L1 / L2. K % 4 == 0.
+__global__ void __launch_bounds__(256) split_rows_f16_kernel(const float* __restrict__ a, int M, int K,
+                                                             __half* __restrict__ hi, __half* __restrict__ lo,
+                                                             float* __restrict__ inv) {
+  const int lane = threadIdx.x & 31;
+  const int K4 = K >> 2;
+  for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < M; row += gridDim.x * 8) {
+    const float4* r4 = reinterpret_cast<const float4*>(a + (size_t)row * K);
+    uint32_t mx = 0;
+    for (int i = lane; i < K4; i += 32) {
+      const float4 v = r4[i];
+      mx = max(max(mx, __float_as_uint(v.x) & 0x7FFFFFFFu), max(max(__float_as_uint(v.y) & 0x7FFFFFFFu,
+               __float_as_uint(v.z) & 0x7FFFFFFFu), __float_as_uint(v.w) & 0x7FFFFFFFu));
+    }
+    mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+    const int e = f16_scale_exp(mx);
+    const float sc = pow2i(e);
+    uint2* h2 = reinterpret_cast<uint2*>(hi + (size_t)row * K);
+    uint2* l2 = reinterpret_cast<uint2*>(lo + (size_t)row * K);
+    for (int i = lane; i < K4; i += 32) {
+      const float4 v = r4[i];
+      float h0, h1, h2f, h3, l0, l1, l2f, l3;
+      split11(v.x * sc, h0, l0);
+      split11(v.y * sc, h1, l1);
+      split11(v.z * sc, h2f, l2f);
+      split11(v.w * sc, h3, l3);
+      h2[i] = make_uint2(pack_h2(h0, h1), pack_h2(h2f, h3));
+      l2[i] = make_uint2(pack_h2(l0, l1), pack_h2(l2f, l3));
+    }
+    if (lane == 0) inv[row] = pow2i(-e);
+  }
+}
+
 // max|x| (as f32 bit patterns, which order like the magnitudes; a NaN sorts above every finite
 // value) of up to four tensors in one launch: blockIdx.y selects the tensor. The slots must be
 // zero beforehand. The maximum does not depend on the order of the atomic updates.
@@ -1711,13 +2036,19 @@ struct TcState {
   bool usable = true;
   float* rank_scratch = nullptr;
   int pair_clusters = 0;          // resident clusters of the pair kernel on this device (0 = not queried yet)
-  int pair_f16_clusters = 0;
+  int pair_f16_clusters = 0, pair_f16p_clusters = 0;
   std::map<const float*, float*> lo_copies;   // frozen B operand -> its precomputed lo part (x - tf32(x))
   struct F16Copy { __half* hi; __half* lo; int exp; };
   std::map<const float*, F16Copy> f16_copies; // frozen B operand -> fp16 split of w * 2^exp (F16X2 mode)
   uint32_t* absmax_dev = nullptr;             // four max|x| slots for the run-time operands of an F16X2 launch
   const float* absmax_src = nullptr;          // the A operand whose maximum slot 0 holds, and when it was measured
   uint64_t absmax_n = 0, absmax_unit = 0;
+  // pre-split A operands of the F16X2 GEMM (sized when programs are built): the main pair's A, the tail's A2
+  __half *a_hi = nullptr, *a_lo = nullptr, *a2_hi = nullptr, *a2_lo = nullptr;
+  float *a_inv = nullptr, *a2_inv = nullptr;
+  uint64_t a_cap = 0, a_rows_cap = 0;           // elements of a_hi / a_lo, rows of the inv arrays and of a2_*
+  const float* split_src = nullptr;             // the A operand a_hi / a_lo currently hold, and when it was split
+  uint64_t split_m = 0, split_k = 0, split_unit = 0;
   __half *tail_hi = nullptr, *tail_lo = nullptr;   // fp16 tiles of the low-rank tail's B operand, [kF16TailRows, 32] each
   std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> maps;
   std::set<const void*> smem_attr_done;   // kernels whose dynamic shared-memory limit was raised on this context's device
@@ -1742,13 +2073,15 @@ const CUtensorMap* cached_map(TcState& st, const void* ptr, uint64_t rows, uint6
   return &st.maps.emplace(key, m).first->second;
 }
 
-// fp16 [rows, cols] row-major: box of box_rows x 32 elements (64-byte rows, 64-byte swizzle).
-const CUtensorMap* cached_map_f16(TcState& st, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  const auto key = std::make_tuple(ptr, rows, cols, box_rows, 0x20000u);
+// fp16 [rows, cols] row-major: box of box_rows x 32 elements (64-byte rows, 64-byte swizzle), or
+// x 64 elements (128-byte rows, 128-byte swizzle) when wide.
+const CUtensorMap* cached_map_f16(TcState& st, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                                  bool wide = false) {
+  const auto key = std::make_tuple(ptr, rows, cols, box_rows, wide ? 0x40000u : 0x20000u);
   auto it = st.maps.find(key);
   if (it != st.maps.end()) return &it->second;
   CUtensorMap m;
-  if (!make_map(&m, ptr, rows, cols, box_rows, 32, 64, true)) return nullptr;
+  if (!make_map(&m, ptr, rows, cols, box_rows, wide ? 64 : 32, wide ? 128 : 64, true)) return nullptr;
   return &st.maps.emplace(key, m).first->second;
 }
 
@@ -1931,6 +2264,85 @@ int launch_pair_f16(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   return 1;
 }
 
+// F16X2 with pre-split operands (see gemm_tc_pair_f16p_kernel). Needs the A scratch sized at build
+// time; anything it cannot take goes to launch_pair_f16.
+int launch_pair_f16p(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
+  auto it = st.f16_copies.find(g.Bt);
+  if (it == st.f16_copies.end() || g.K2 > 32 || (g.K2 % 8) != 0 || g.N > kF16TailRows || g.K % 8 != 0 ||
+      g.M * g.K > st.a_cap || g.M > st.a_rows_cap || !st.a_hi)
+    return launch_pair_f16(c, st, g);
+  if (!ensure_smem_attr(st, gemm_tc_pair_f16p_kernel, PairF16pSmem::kTotal)) return -1;
+  if (!st.absmax_dev || !st.tail_hi) {
+    if ((!st.absmax_dev && cudaMalloc(&st.absmax_dev, 64) != cudaSuccess) ||
+        (!st.tail_hi && cudaMalloc(&st.tail_hi, 2 * kF16TailRows * 32 * sizeof(__half)) != cudaSuccess)) {
+      cudaGetLastError();
+      return -1;
+    }
+    st.tail_lo = st.tail_hi + kF16TailRows * 32;
+  }
+  const CUtensorMap* mah = cached_map_f16(st, st.a_hi, g.M, g.K, BM, true);
+  const CUtensorMap* mal = cached_map_f16(st, st.a_lo, g.M, g.K, BM, true);
+  const CUtensorMap* ma2h = g.K2 ? cached_map_f16(st, st.a2_hi, g.M, g.K2, BM, true) : mah;
+  const CUtensorMap* ma2l = g.K2 ? cached_map_f16(st, st.a2_lo, g.M, g.K2, BM, true) : mal;
+  const CUtensorMap* mbh = cached_map_f16(st, it->second.hi, g.N, g.K, 128, true);
+  const CUtensorMap* mbl = cached_map_f16(st, it->second.lo, g.N, g.K, 128, true);
+  const CUtensorMap* mb2h = g.K2 ? cached_map_f16(st, st.tail_hi, g.N, 32, 128, true) : mbh;
+  const CUtensorMap* mb2l = g.K2 ? cached_map_f16(st, st.tail_lo, g.N, 32, 128, true) : mbl;
+  const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
+  if (!mah || !mal || !ma2h || !ma2l || !mbh || !mbl || !mb2h || !mb2l || !mc) return -1;
+  // the previous unit of the same run split the same A (q / k / v, gate / up): nothing wrote it since
+  const bool reuse = st.split_src == g.A && st.split_m == g.M && st.split_k == g.K &&
+                     (c->exec_unit == st.split_unit || c->exec_unit == st.split_unit + 1);
+  st.split_src = g.A; st.split_m = g.M; st.split_k = g.K; st.split_unit = c->exec_unit;
+  const unsigned row_blocks = (unsigned)std::min<uint64_t>((g.M + 7) / 8, 148 * 16);
+  if (!reuse)
+    split_rows_f16_kernel<<<row_blocks, 256, 0, c->stream>>>(g.A, (int)g.M, (int)g.K, st.a_hi, st.a_lo, st.a_inv);
+  if (g.K2) {
+    split_rows_f16_kernel<<<row_blocks, 256, 0, c->stream>>>(g.A2, (int)g.M, (int)g.K2, st.a2_hi, st.a2_lo, st.a2_inv);
+    AbsmaxArgs aa{};
+    aa.ptr[3] = g.B2t; aa.n[3] = g.N * g.K2;
+    if (cudaMemsetAsync(st.absmax_dev, 0, 16, c->stream) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+    absmax4_kernel<<<dim3(32, 4), 256, 0, c->stream>>>(aa, st.absmax_dev);
+    split_f16_tail_kernel<<<(unsigned)((g.N * 32 + 255) / 256), 256, 0, c->stream>>>(g.B2t, st.tail_hi, st.tail_lo, (int)g.N,
+                                                                                  (int)g.K2, st.absmax_dev + 3);
+  }
+  F16pParams p{};
+  p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.K2 = (int)g.K2;
+  p.bias = g.bias; p.addend = g.addend; p.act = g.act; p.alpha = g.alpha == 0.0f ? 1.0f : g.alpha;
+  p.eb_pre = it->second.exp; p.inv_a = st.a_inv; p.inv_a2 = st.a2_inv; p.absmax = st.absmax_dev; p.err = st.err_dev;
+  p.n_tiles = (int)((g.N + 255) / 256);
+  p.total_tiles = p.n_tiles * (int)(((g.M + BM - 1) / BM) / 2);
+  cudaLaunchConfig_t cfg{};
+  cfg.blockDim = dim3(kThreadsV2);
+  cfg.dynamicSmemBytes = PairF16pSmem::kTotal;
+  cfg.stream = c->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (st.pair_f16p_clusters == 0) {
+    cfg.gridDim = dim3(2u * 1024u);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_f16p_kernel, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 74;
+    }
+    st.pair_f16p_clusters = n;
+  }
+  cfg.gridDim = dim3(2u * (unsigned)std::min(p.total_tiles, st.pair_f16p_clusters));
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_pair_f16p_kernel, *mah, *mal, *ma2h, *ma2l, *mbh, *mbl, *mb2h,
+                                            *mb2l, *mc, p);
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return 1;
+}
+
 TcState* state_of(seeml_b200_ctx* c, bool create) {
   auto it = states().find(c);
   if (it == states().end()) {
@@ -1963,7 +2375,9 @@ int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g) {
   static const bool half_blocks = [] { const char* e = std::getenv("SEEML_B200_GEMM_KB"); return e && std::atoi(e) == 16; }();
   static const bool pairs = [] { const char* e = std::getenv("SEEML_B200_GEMM_PAIR"); return !e || std::atoi(e) != 0; }();
   const uint64_t m_tiles = (g.M + BM - 1) / BM;
-  if (g.N >= 192 && pairs && m_tiles % 2 == 0 && c->gemm_kind == SEEML_B200_GEMM_F16X2) r = launch_pair_f16(c, *st, g);
+  static const bool presplit = [] { const char* e = std::getenv("SEEML_B200_F16_PRESPLIT"); return !e || std::atoi(e) != 0; }();
+  if (g.N >= 192 && pairs && m_tiles % 2 == 0 && c->gemm_kind == SEEML_B200_GEMM_F16X2)
+    r = presplit ? launch_pair_f16p(c, *st, g) : launch_pair_f16(c, *st, g);
   else if (g.N >= 192 && split && pairs && m_tiles % 2 == 0) r = launch_pair(c, *st, g);
   else if (g.N >= 192 && split && half_blocks) r = launch_tc<256, true, 4, 16>(c, *st, g);
   else if (g.N >= 192) r = split ? launch_tc<256, true, 2>(c, *st, g) : launch_tc<256, false, 4>(c, *st, g);
@@ -2235,10 +2649,41 @@ static bool tc_instr(const seeml_b200_ctx* c, const Instr& ins) {
   return gemm_tc_shape_ok(c, ins.out[0], ins.out[1], ins.out[2]);
 }
 
+// Scratch for the pre-split A operands of the F16X2 GEMM: grown when a program with a larger
+// GEMM is built (never while running). Growing replaces buffers whose addresses captured graphs
+// hold, so every graph of the context is dropped first.
+static int ensure_a_split(seeml_b200_ctx* c, TcState& st, uint64_t M, uint64_t K) {
+  if (M * K <= st.a_cap && M <= st.a_rows_cap) return 0;
+  const uint64_t cap = std::max(st.a_cap, M * K), rows = std::max(st.a_rows_cap, M);
+  cudaStreamSynchronize(c->stream);
+  drop_graphs(c);
+  st.maps.clear();                      // tensor maps of the old buffers
+  st.split_src = nullptr;
+  cudaFree(st.a_hi); cudaFree(st.a_lo); cudaFree(st.a2_hi); cudaFree(st.a2_lo); cudaFree(st.a_inv); cudaFree(st.a2_inv);
+  st.a_hi = st.a_lo = st.a2_hi = st.a2_lo = nullptr;
+  st.a_inv = st.a2_inv = nullptr;
+  st.a_cap = st.a_rows_cap = 0;
+  if (cudaMalloc(&st.a_hi, cap * 2) != cudaSuccess || cudaMalloc(&st.a_lo, cap * 2) != cudaSuccess ||
+      cudaMalloc(&st.a2_hi, rows * 32 * 2) != cudaSuccess || cudaMalloc(&st.a2_lo, rows * 32 * 2) != cudaSuccess ||
+      cudaMalloc(&st.a_inv, rows * 4) != cudaSuccess || cudaMalloc(&st.a2_inv, rows * 4) != cudaSuccess) {
+    cudaGetLastError();                 // not fatal: the launcher falls back to the in-kernel split
+    cudaFree(st.a_hi); cudaFree(st.a_lo); cudaFree(st.a2_hi); cudaFree(st.a2_lo); cudaFree(st.a_inv); cudaFree(st.a2_inv);
+    st.a_hi = st.a_lo = st.a2_hi = st.a2_lo = nullptr;
+    st.a_inv = st.a2_inv = nullptr;
+    return 0;
+  }
+  st.a_cap = cap;
+  st.a_rows_cap = rows;
+  return 0;
+}
+
 int gemm_tensor_core_prepare(seeml_b200_ctx* c, const Instr& ins) {
   if (c->gemm_kind == SEEML_B200_GEMM_FP32_SIMT) return 0;
-  if (!state_of(c, true)) return cuda_fail(cudaGetLastError(), "tc error word");
+  TcState* stp = state_of(c, true);
+  if (!stp) return cuda_fail(cudaGetLastError(), "tc error word");
   if (!tc_instr(c, ins)) return 0;
+  if (c->gemm_kind == SEEML_B200_GEMM_F16X2 && ins.out[1] >= 192 && ((ins.out[0] + BM - 1) / BM) % 2 == 0)
+    ensure_a_split(c, *stp, ins.out[0], ins.out[2]);
   if (ins.opcode == kGemmNN) {
     const float* wt = gemm_tc_transposed_weight(c, ref_off(ins.in[1]), ins.out[2], ins.out[1], true);
     if (!wt) return fail("UpdateEngine: transposed weight allocation failed");
@@ -2293,6 +2738,8 @@ void gemm_tensor_core_release(seeml_b200_ctx* c) {
   }
   cudaFree(sit->second.absmax_dev);
   cudaFree(sit->second.tail_hi);
+  cudaFree(sit->second.a_hi); cudaFree(sit->second.a_lo); cudaFree(sit->second.a2_hi); cudaFree(sit->second.a2_lo);
+  cudaFree(sit->second.a_inv); cudaFree(sit->second.a2_inv);
   states().erase(sit);
 }
 

@@ -349,6 +349,51 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bwd_kernel(
   }
 }
 
+// The same backward with the row held in registers between the reduction and the output sweep
+// (one warp per row, cols = 128 * NV): dy and x are read from memory once. Element-to-lane
+// assignment and accumulation order equal the generic kernel's, so do the bits.
+template <int NV>
+__global__ void __launch_bounds__(kThreads) rmsnorm_bwd_regs_kernel(
+    const float* dy, const float* x, const float* __restrict__ g, const float* __restrict__ rstd, float* dx,
+    const float* addend, size_t rows) {
+  constexpr size_t cols = 128 * NV;
+  const int lane = threadIdx.x & 31;
+  const size_t rpb = kThreads / 32;
+  const float inv_d = 1.0f / (float)cols;
+  for (size_t r = blockIdx.x * rpb + (threadIdx.x >> 5); r < rows; r += (size_t)gridDim.x * rpb) {
+    float4 d4[NV], x4[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      d4[i] = reinterpret_cast<const float4*>(dy + r * cols)[lane + 32 * i];
+      x4[i] = reinterpret_cast<const float4*>(x + r * cols)[lane + 32 * i];
+    }
+    const float rs = rstd[r];
+    double sgx = 0.0;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const float4 g4 = reinterpret_cast<const float4*>(g)[lane + 32 * i];
+      sgx += (double)(d4[i].x * g4.x) * x4[i].x + (double)(d4[i].y * g4.y) * x4[i].y +
+             (double)(d4[i].z * g4.z) * x4[i].z + (double)(d4[i].w * g4.w) * x4[i].w;
+    }
+    sgx = warp_sum(sgx);
+    const float mgx = (float)sgx * inv_d;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const float4 g4 = reinterpret_cast<const float4*>(g)[lane + 32 * i];
+      float4 o;
+      o.x = rs * (d4[i].x * g4.x - x4[i].x * rs * rs * mgx);
+      o.y = rs * (d4[i].y * g4.y - x4[i].y * rs * rs * mgx);
+      o.z = rs * (d4[i].z * g4.z - x4[i].z * rs * rs * mgx);
+      o.w = rs * (d4[i].w * g4.w - x4[i].w * rs * rs * mgx);
+      if (addend != nullptr) {
+        const float4 a4 = reinterpret_cast<const float4*>(addend + r * cols)[lane + 32 * i];
+        o.x = a4.x + o.x; o.y = a4.y + o.y; o.z = a4.z + o.z; o.w = a4.w + o.w;
+      }
+      reinterpret_cast<float4*>(dx + r * cols)[lane + 32 * i] = o;
+    }
+  }
+}
+
 // ---- RoPE: one thread per interleaved pair ------------------------------------------------
 __global__ void __launch_bounds__(kThreads) rope_kernel(const float2* __restrict__ x,
                                                         float2* __restrict__ y,
@@ -458,30 +503,59 @@ inline size_t row_grain(size_t per_row, size_t budget) {
 
 // Row softmax (f32 max-subtracted; the denominator is summed in double and rounded once)
 // + per-row loss term -log(max(p[label],1e-12)) in double, NaN kept. One block per row.
+// With vec (C % 4 == 0, 16-byte aligned rows) the sweeps use 128-bit accesses; the element-to-thread
+// assignment then differs from the scalar path, which only moves the last bits of the double sum.
 template <int TPR>
 __global__ void __launch_bounds__(kThreads) xent_rows_kernel(
     const float* __restrict__ logits, const int32_t* __restrict__ labels,
-    float* __restrict__ probs, double* __restrict__ terms, size_t N, size_t C, float inv_T) {
+    float* __restrict__ probs, double* __restrict__ terms, size_t N, size_t C, float inv_T, int vec) {
   __shared__ double smd[8];
   __shared__ float smf[8];
   const int lane = TPR == 32 ? (threadIdx.x & 31) : threadIdx.x;
   const size_t rpb = kThreads / TPR;
   const size_t row0 = blockIdx.x * rpb + (TPR == 32 ? (threadIdx.x >> 5) : 0);
+  const size_t C4 = C >> 2;
   for (size_t n = row0; n < N; n += (size_t)gridDim.x * rpb) {
     const float* z = logits + n * C;
     float* p = probs + n * C;
     float mx = -INFINITY;
-    for (size_t c = lane; c < C; c += TPR) mx = fmaxf(mx, z[c] * inv_T);
+    if (vec) {
+      for (size_t c = lane; c < C4; c += TPR) {
+        const float4 v = reinterpret_cast<const float4*>(z)[c];
+        mx = fmaxf(fmaxf(mx, fmaxf(v.x * inv_T, v.y * inv_T)), fmaxf(v.z * inv_T, v.w * inv_T));
+      }
+    } else {
+      for (size_t c = lane; c < C; c += TPR) mx = fmaxf(mx, z[c] * inv_T);
+    }
     mx = row_max<TPR>(mx, smf);
     double sum = 0.0;
-    for (size_t c = lane; c < C; c += TPR) {
-      const float e = expf(z[c] * inv_T - mx);
-      p[c] = e;
-      sum += e;
+    if (vec) {
+      for (size_t c = lane; c < C4; c += TPR) {
+        const float4 v = reinterpret_cast<const float4*>(z)[c];
+        float4 e;
+        e.x = expf(v.x * inv_T - mx); e.y = expf(v.y * inv_T - mx);
+        e.z = expf(v.z * inv_T - mx); e.w = expf(v.w * inv_T - mx);
+        reinterpret_cast<float4*>(p)[c] = e;
+        sum += e.x; sum += e.y; sum += e.z; sum += e.w;
+      }
+    } else {
+      for (size_t c = lane; c < C; c += TPR) {
+        const float e = expf(z[c] * inv_T - mx);
+        p[c] = e;
+        sum += e;
+      }
     }
     sum = row_sum<TPR>(sum, smd);
     const float inv = 1.0f / (float)sum;
-    for (size_t c = lane; c < C; c += TPR) p[c] *= inv;
+    if (vec) {
+      for (size_t c = lane; c < C4; c += TPR) {
+        float4 e = reinterpret_cast<float4*>(p)[c];
+        e.x *= inv; e.y *= inv; e.z *= inv; e.w *= inv;
+        reinterpret_cast<float4*>(p)[c] = e;
+      }
+    } else {
+      for (size_t c = lane; c < C; c += TPR) p[c] *= inv;
+    }
     if (labels != nullptr) {
       if (TPR != 32) __syncthreads();
       else __syncwarp();
@@ -717,23 +791,41 @@ __global__ void __launch_bounds__(kThreads) swiglu_bwd_kernel(const float4* dm, 
 template <int TPR>
 __global__ void __launch_bounds__(kThreads) xent_fused_rows_kernel(
     const float* logits, const int32_t* __restrict__ labels, float* probs, float* d,
-    double* __restrict__ terms, size_t N, size_t C, float scale) {
+    double* __restrict__ terms, size_t N, size_t C, float scale, int vec) {
   __shared__ double smd[8];
   __shared__ float smf[8];
   const int lane = TPR == 32 ? (threadIdx.x & 31) : threadIdx.x;
   const size_t rpb = kThreads / TPR;
   const size_t row0 = blockIdx.x * rpb + (TPR == 32 ? (threadIdx.x >> 5) : 0);
+  const size_t C4 = C >> 2;
   for (size_t n = row0; n < N; n += (size_t)gridDim.x * rpb) {
     const float* z = logits + n * C;
     float* e = d + n * C;
     float mx = -INFINITY;
-    for (size_t c = lane; c < C; c += TPR) mx = fmaxf(mx, z[c]);
+    if (vec) {
+      for (size_t c = lane; c < C4; c += TPR) {
+        const float4 v = reinterpret_cast<const float4*>(z)[c];
+        mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+      }
+    } else {
+      for (size_t c = lane; c < C; c += TPR) mx = fmaxf(mx, z[c]);
+    }
     mx = row_max<TPR>(mx, smf);
     double sum = 0.0;
-    for (size_t c = lane; c < C; c += TPR) {
-      const float ev = expf(z[c] - mx);
-      e[c] = ev;
-      sum += ev;
+    if (vec) {
+      for (size_t c = lane; c < C4; c += TPR) {
+        const float4 v = reinterpret_cast<const float4*>(z)[c];
+        float4 ev;
+        ev.x = expf(v.x - mx); ev.y = expf(v.y - mx); ev.z = expf(v.z - mx); ev.w = expf(v.w - mx);
+        reinterpret_cast<float4*>(e)[c] = ev;
+        sum += ev.x; sum += ev.y; sum += ev.z; sum += ev.w;
+      }
+    } else {
+      for (size_t c = lane; c < C; c += TPR) {
+        const float ev = expf(z[c] - mx);
+        e[c] = ev;
+        sum += ev;
+      }
     }
     sum = row_sum<TPR>(sum, smd);
     const float inv = 1.0f / (float)sum;
@@ -747,12 +839,30 @@ __global__ void __launch_bounds__(kThreads) xent_fused_rows_kernel(
     }
     if (TPR != 32) __syncthreads();
     else __syncwarp();
-    for (size_t c = lane; c < C; c += TPR) {
-      const float p = e[c] * inv;
-      if (probs != nullptr) probs[n * C + c] = p;
-      float v = scale * p;
-      if (c == lab) v -= scale;
-      e[c] = v;
+    if (vec) {
+      for (size_t c = lane; c < C4; c += TPR) {
+        float4 pv = reinterpret_cast<float4*>(e)[c];
+        pv.x *= inv; pv.y *= inv; pv.z *= inv; pv.w *= inv;
+        if (probs != nullptr) reinterpret_cast<float4*>(probs + n * C)[c] = pv;
+        float4 v;
+        v.x = scale * pv.x; v.y = scale * pv.y; v.z = scale * pv.z; v.w = scale * pv.w;
+        const size_t k = (size_t)lab - 4 * c;
+        if (k < 4) {
+          if (k == 0) v.x -= scale;
+          else if (k == 1) v.y -= scale;
+          else if (k == 2) v.z -= scale;
+          else v.w -= scale;
+        }
+        reinterpret_cast<float4*>(e)[c] = v;
+      }
+    } else {
+      for (size_t c = lane; c < C; c += TPR) {
+        const float p = e[c] * inv;
+        if (probs != nullptr) probs[n * C + c] = p;
+        float v = scale * p;
+        if (c == lab) v -= scale;
+        e[c] = v;
+      }
     }
   }
 }
@@ -927,6 +1037,13 @@ int rmsnorm_bwd(const float* dy, const float* x, const float* g, const float* rs
   if (rows == 0) return 0;
   const int vec = cols % 4 == 0 && aligned16(x) && aligned16(g) && aligned16(dy) && aligned16(dx) &&
                   (addend == nullptr || aligned16(addend));
+  if (vec && cols % 128 == 0 && cols <= 1024) {
+    const int grid = grid_for(rows, kThreads / 32, 16);
+#define RMS_REGS(NV) case NV: rmsnorm_bwd_regs_kernel<NV><<<grid, kThreads, 0, st>>>(dy, x, g, rstd, dx, addend, rows); break;
+    switch (cols / 128) { RMS_REGS(1) RMS_REGS(2) RMS_REGS(3) RMS_REGS(4) RMS_REGS(5) RMS_REGS(6) RMS_REGS(7) RMS_REGS(8) }
+#undef RMS_REGS
+    return 1;
+  }
   ROW_LAUNCH(rmsnorm_bwd_kernel, rows, cols, dy, x, g, rstd, dx, addend, rows, cols, vec);
   return 1;
 }
@@ -960,6 +1077,13 @@ int softmax_rows_bwd(const float* P, const float* dP, float* dS, size_t rows, si
 
 size_t loss_scratch_doubles(size_t rows_or_elems) { return rows_or_elems + 256; }
 
+// Blocks per SM of the row-per-block softmax kernels: the rows in flight (three sweeps each) should
+// stay in L2 together, about 48 MB of them.
+static int xent_waves(size_t C) {
+  const size_t per_sm = (48u << 20) / (C * 4 * kSMs + 1);
+  return (int)(per_sm < 1 ? 1 : (per_sm > 16 ? 16 : per_sm));
+}
+
 static int finish_loss(double* terms, size_t n_terms, size_t grain, double denom, float* loss,
                        cudaStream_t st) {
   // terms -> chunk partials (chunk geometry = the reference's) -> ordered sum -> mean
@@ -972,12 +1096,13 @@ static int finish_loss(double* terms, size_t n_terms, size_t grain, double denom
 int xent_fwd(const float* logits, const int32_t* labels, float* loss, float* probs, size_t N,
              size_t C, double* scratch, cudaStream_t st) {
   if (N == 0) return 0;
+  const int vec = C % 4 == 0 && aligned16(logits) && aligned16(probs);
   if (C <= 1024)
     xent_rows_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(logits, labels, probs,
-                                                                             scratch, N, C, 1.0f);
+                                                                             scratch, N, C, 1.0f, vec);
   else
-    xent_rows_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(logits, labels, probs,
-                                                                       scratch, N, C, 1.0f);
+    xent_rows_kernel<kThreads><<<grid_for(N, 1, xent_waves(C)), kThreads, 0, st>>>(logits, labels, probs,
+                                                                                  scratch, N, C, 1.0f, vec);
   return 1 + finish_loss(scratch, N, chunk_grain(N, row_grain(C, 4096)), (double)N, loss, st);
 }
 int xent_bwd(const float* probs, const int32_t* labels, const float* seed, float* dlogits,
@@ -1009,12 +1134,12 @@ int kl_fwd(const float* s, const float* t, float* loss, float* ps, float* pt, si
   if (N == 0) return 0;
   const float inv_T = 1.0f / T;
   if (C <= 1024) {
-    xent_rows_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(s, nullptr, ps, scratch, N, C, inv_T);
-    xent_rows_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(t, nullptr, pt, scratch, N, C, inv_T);
+    xent_rows_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(s, nullptr, ps, scratch, N, C, inv_T, 0);
+    xent_rows_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(t, nullptr, pt, scratch, N, C, inv_T, 0);
     kl_terms_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(ps, pt, scratch, N, C);
   } else {
-    xent_rows_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(s, nullptr, ps, scratch, N, C, inv_T);
-    xent_rows_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(t, nullptr, pt, scratch, N, C, inv_T);
+    xent_rows_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(s, nullptr, ps, scratch, N, C, inv_T, 0);
+    xent_rows_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(t, nullptr, pt, scratch, N, C, inv_T, 0);
     kl_terms_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(ps, pt, scratch, N, C);
   }
   return 3 + finish_loss(scratch, N, chunk_grain(N, row_grain(C, 4096)), (double)N, loss, st);
@@ -1067,12 +1192,13 @@ int xent_fused(const float* logits, const int32_t* labels, float* loss, float* p
                size_t N, size_t C, double* scratch, cudaStream_t st) {
   if (N == 0) return 0;
   const float scale = seed / (float)N;
+  const int vec = C % 4 == 0 && aligned16(logits) && aligned16(dlogits) && (probs == nullptr || aligned16(probs));
   if (C <= 1024)
     xent_fused_rows_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(logits, labels, probs, dlogits,
-                                                                                   scratch, N, C, scale);
+                                                                                   scratch, N, C, scale, vec);
   else
-    xent_fused_rows_kernel<kThreads><<<grid_for(N, 1, 16), kThreads, 0, st>>>(logits, labels, probs, dlogits,
-                                                                             scratch, N, C, scale);
+    xent_fused_rows_kernel<kThreads><<<grid_for(N, 1, xent_waves(C)), kThreads, 0, st>>>(logits, labels, probs, dlogits,
+                                                                                        scratch, N, C, scale, vec);
   return 1 + finish_loss(scratch, N, chunk_grain(N, row_grain(C, 4096)), (double)N, loss, st);
 }
 int adamw_multi(const AdamwDesc* descs_dev, int ndesc, unsigned total_blocks, const DevScalars* sc, cudaStream_t st) {

@@ -82,7 +82,7 @@ def test_generated_driver_reports_a_missing_gpu_as_a_load_error(tmp_path):
 
 def _python_path(blob, sds, smf, out, steps, seed, val_frac, mode):
     from see_ml_b200.engine import Dataset, UpdateEngine
-    e = UpdateEngine(0, mode, 0)
+    e = UpdateEngine(0, mode, 1)
     e.load_from_memory(blob)
     ds = Dataset.load_from_file(sds)
     val = ds.split_validation(val_frac)
@@ -103,7 +103,7 @@ def test_model_update_trains_gates_merges_and_commits_like_the_python_path(tmp_p
     exe, smf, sds, blob, _ = _package(tmp_path, pc)
     out, log = str(tmp_path / "updated.smf"), str(tmp_path / "curve.csv")
     r = _run(exe, "--model", smf, "--data", sds, "--out", out, "--steps", "40", "--seed", "7", "--val-frac", "0.2",
-             "--loss-log", log, env={"SEEML_B200_MODE": "fused"})
+             "--loss-log", log, env={"SEEML_B200_MODE": "fused", "SEEML_B200_GEMM": "f16x2"})
     assert r.returncode == 0, r.stderr
     assert "seeml-update: committed" in r.stderr and "validation loss" in r.stderr
     want_out = str(tmp_path / "updated_py.smf")
