@@ -1315,7 +1315,7 @@ struct F16pParams {
   int eb_pre;                  // scale exponent of the frozen B copies
   const float* inv_a;          // [M]: 2^-e of each row of A (main pair)
   const float* inv_a2;         // [M]: the same for the tail's A2
-  const uint32_t* absmax;      // slot 3: max|x| of the tail's B2 (its copies hold B2 * 2^e)
+  const float* inv_b2;         // [N]: and for each row of the tail's B2 (an output column)
   int n_tiles, total_tiles;
   int* err;
 };
@@ -1476,7 +1476,7 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
     // ---- worker warps (both CTAs): collect finished chunks, epilogue ----------------------------
     const int q = warp & 3, half = (warp - 2) >> 2, row0 = q * 32;
     constexpr int NH = BN / 2, LD = 32;
-    const float inv_b = pow2i(-p.eb_pre), inv_b2 = pow2i(-f16_scale_exp(p.absmax[3]));
+    const float inv_b = pow2i(-p.eb_pre);
     float acc[NH];
     bool ok = true;
     int cg = 0, tiles_done = 0;
@@ -1485,7 +1485,7 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
       tile_of(tl, m0, n0);
       const int m = m0 + row0 + lane;
       const float cs_main = (m < p.M ? p.inv_a[m] : 1.0f) * inv_b;
-      const float cs_tail = (p.K2 && m < p.M ? p.inv_a2[m] : 1.0f) * inv_b2;
+      const float cs_tail = p.K2 && m < p.M ? p.inv_a2[m] : 1.0f;
 #pragma unroll
       for (int j = 0; j < NH; ++j) acc[j] = 0.0f;
       for (int ci = 0; ci < nchunks && ok; ++ci, ++cg) {
@@ -1493,14 +1493,20 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
         ok = mbar_wait(bar_acc_full(buf), (cg >> 1) & 1, p.err, 54);
         if (!ok) break;
         tc_fence_after();
-        const float cs = ci < nmain ? cs_main : cs_tail;
 #pragma unroll
         for (int c = 0; c < NH / LD; ++c) {
           uint32_t r[32];
           tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + buf * BN + half * NH + c * LD, r);
           tmem_ld_wait();
+          if (ci < nmain) {
 #pragma unroll
-          for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]) * cs;
+            for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]) * cs_main;
+          } else {            // the tail's B2 is scaled per row of B2, i.e. per output column
+            const int col0 = n0 + half * NH + c * LD;
+#pragma unroll
+            for (int j = 0; j < LD; ++j)
+              acc[c * LD + j] += __uint_as_float(r[j]) * (cs_tail * (col0 + j < p.N ? __ldg(p.inv_b2 + col0 + j) : 1.0f));
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -1577,36 +1583,41 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
 // One pass over a row-major f32 tensor [M, K]: each row's largest magnitude picks its power-of-two
 // scale 2^e (max * 2^e in [2^13, 2^14)), the row is cut into fp16 hi = fp16(x 2^e) and
 // lo = fp16(x 2^e - hi), and 2^-e goes to inv[row]. One warp per row; the second sweep over the
-// row comes from L1 / L2. K % 4 == 0.
-__global__ void __launch_bounds__(256) split_rows_f16_kernel(const float* __restrict__ a, int M, int K,
-                                                             __half* __restrict__ hi, __half* __restrict__ lo,
-                                                             float* __restrict__ inv) {
+// row comes from L1 / L2. K % 4 == 0. Up to two tensors per launch (the low-rank tail's two small
+// operands go together): rows [0, a.M) are the first tensor's, the rest the second's.
+struct SplitJob { const float* src; __half* hi; __half* lo; float* inv; int M, K; };
+__device__ __forceinline__ void split_row_f16(const SplitJob& t, int row, int lane) {
+  const int K4 = t.K >> 2;
+  const float4* r4 = reinterpret_cast<const float4*>(t.src + (size_t)row * t.K);
+  uint32_t mx = 0;
+  for (int i = lane; i < K4; i += 32) {
+    const float4 v = r4[i];
+    mx = max(max(mx, __float_as_uint(v.x) & 0x7FFFFFFFu), max(max(__float_as_uint(v.y) & 0x7FFFFFFFu,
+             __float_as_uint(v.z) & 0x7FFFFFFFu), __float_as_uint(v.w) & 0x7FFFFFFFu));
+  }
+  mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+  const int e = f16_scale_exp(mx);
+  const float sc = pow2i(e);
+  uint2* h2 = reinterpret_cast<uint2*>(t.hi + (size_t)row * t.K);
+  uint2* l2 = reinterpret_cast<uint2*>(t.lo + (size_t)row * t.K);
+  for (int i = lane; i < K4; i += 32) {
+    const float4 v = r4[i];
+    float h0, h1, h2f, h3, l0, l1, l2f, l3;
+    split11(v.x * sc, h0, l0);
+    split11(v.y * sc, h1, l1);
+    split11(v.z * sc, h2f, l2f);
+    split11(v.w * sc, h3, l3);
+    h2[i] = make_uint2(pack_h2(h0, h1), pack_h2(h2f, h3));
+    l2[i] = make_uint2(pack_h2(l0, l1), pack_h2(l2f, l3));
+  }
+  if (lane == 0) t.inv[row] = pow2i(-e);
+}
+__global__ void __launch_bounds__(256) split_rows_f16_kernel(SplitJob a, SplitJob b) {
   const int lane = threadIdx.x & 31;
-  const int K4 = K >> 2;
-  for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < M; row += gridDim.x * 8) {
-    const float4* r4 = reinterpret_cast<const float4*>(a + (size_t)row * K);
-    uint32_t mx = 0;
-    for (int i = lane; i < K4; i += 32) {
-      const float4 v = r4[i];
-      mx = max(max(mx, __float_as_uint(v.x) & 0x7FFFFFFFu), max(max(__float_as_uint(v.y) & 0x7FFFFFFFu,
-               __float_as_uint(v.z) & 0x7FFFFFFFu), __float_as_uint(v.w) & 0x7FFFFFFFu));
-    }
-    mx = __reduce_max_sync(0xFFFFFFFFu, mx);
-    const int e = f16_scale_exp(mx);
-    const float sc = pow2i(e);
-    uint2* h2 = reinterpret_cast<uint2*>(hi + (size_t)row * K);
-    uint2* l2 = reinterpret_cast<uint2*>(lo + (size_t)row * K);
-    for (int i = lane; i < K4; i += 32) {
-      const float4 v = r4[i];
-      float h0, h1, h2f, h3, l0, l1, l2f, l3;
-      split11(v.x * sc, h0, l0);
-      split11(v.y * sc, h1, l1);
-      split11(v.z * sc, h2f, l2f);
-      split11(v.w * sc, h3, l3);
-      h2[i] = make_uint2(pack_h2(h0, h1), pack_h2(h2f, h3));
-      l2[i] = make_uint2(pack_h2(l0, l1), pack_h2(l2f, l3));
-    }
-    if (lane == 0) inv[row] = pow2i(-e);
+  const int total = a.M + b.M;
+  for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total; row += gridDim.x * 8) {
+    if (row < a.M) split_row_f16(a, row, lane);
+    else split_row_f16(b, row - a.M, lane);
   }
 }
 
@@ -2049,7 +2060,8 @@ struct TcState {
   uint64_t a_cap = 0, a_rows_cap = 0;           // elements of a_hi / a_lo, rows of the inv arrays and of a2_*
   const float* split_src = nullptr;             // the A operand a_hi / a_lo currently hold, and when it was split
   uint64_t split_m = 0, split_k = 0, split_unit = 0;
-  __half *tail_hi = nullptr, *tail_lo = nullptr;   // fp16 tiles of the low-rank tail's B operand, [kF16TailRows, 32] each
+  __half *tail_hi = nullptr, *tail_lo = nullptr;
+  float* tail_inv = nullptr;                    // per-row 2^-e of the pre-split tail operand   // fp16 tiles of the low-rank tail's B operand, [kF16TailRows, 32] each
   std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> maps;
   std::set<const void*> smem_attr_done;   // kernels whose dynamic shared-memory limit was raised on this context's device
 };
@@ -2272,9 +2284,9 @@ int launch_pair_f16p(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
       g.M * g.K > st.a_cap || g.M > st.a_rows_cap || !st.a_hi)
     return launch_pair_f16(c, st, g);
   if (!ensure_smem_attr(st, gemm_tc_pair_f16p_kernel, PairF16pSmem::kTotal)) return -1;
-  if (!st.absmax_dev || !st.tail_hi) {
-    if ((!st.absmax_dev && cudaMalloc(&st.absmax_dev, 64) != cudaSuccess) ||
-        (!st.tail_hi && cudaMalloc(&st.tail_hi, 2 * kF16TailRows * 32 * sizeof(__half)) != cudaSuccess)) {
+  if (!st.tail_hi || !st.tail_inv) {
+    if ((!st.tail_hi && cudaMalloc(&st.tail_hi, 2 * kF16TailRows * 32 * sizeof(__half)) != cudaSuccess) ||
+        (!st.tail_inv && cudaMalloc(&st.tail_inv, kF16TailRows * sizeof(float)) != cudaSuccess)) {
       cudaGetLastError();
       return -1;
     }
@@ -2286,33 +2298,28 @@ int launch_pair_f16p(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   const CUtensorMap* ma2l = g.K2 ? cached_map_f16(st, st.a2_lo, g.M, g.K2, BM, true) : mal;
   const CUtensorMap* mbh = cached_map_f16(st, it->second.hi, g.N, g.K, 128, true);
   const CUtensorMap* mbl = cached_map_f16(st, it->second.lo, g.N, g.K, 128, true);
-  const CUtensorMap* mb2h = g.K2 ? cached_map_f16(st, st.tail_hi, g.N, 32, 128, true) : mbh;
-  const CUtensorMap* mb2l = g.K2 ? cached_map_f16(st, st.tail_lo, g.N, 32, 128, true) : mbl;
+  const CUtensorMap* mb2h = g.K2 ? cached_map_f16(st, st.tail_hi, g.N, g.K2, 128, true) : mbh;
+  const CUtensorMap* mb2l = g.K2 ? cached_map_f16(st, st.tail_lo, g.N, g.K2, 128, true) : mbl;
   const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
   if (!mah || !mal || !ma2h || !ma2l || !mbh || !mbl || !mb2h || !mb2l || !mc) return -1;
   // the previous unit of the same run split the same A (q / k / v, gate / up): nothing wrote it since
   const bool reuse = st.split_src == g.A && st.split_m == g.M && st.split_k == g.K &&
                      (c->exec_unit == st.split_unit || c->exec_unit == st.split_unit + 1);
   st.split_src = g.A; st.split_m = g.M; st.split_k = g.K; st.split_unit = c->exec_unit;
-  const unsigned row_blocks = (unsigned)std::min<uint64_t>((g.M + 7) / 8, 148 * 16);
-  if (!reuse)
-    split_rows_f16_kernel<<<row_blocks, 256, 0, c->stream>>>(g.A, (int)g.M, (int)g.K, st.a_hi, st.a_lo, st.a_inv);
-  if (g.K2) {
-    split_rows_f16_kernel<<<row_blocks, 256, 0, c->stream>>>(g.A2, (int)g.M, (int)g.K2, st.a2_hi, st.a2_lo, st.a2_inv);
-    AbsmaxArgs aa{};
-    aa.ptr[3] = g.B2t; aa.n[3] = g.N * g.K2;
-    if (cudaMemsetAsync(st.absmax_dev, 0, 16, c->stream) != cudaSuccess) {
-      cudaGetLastError();
-      return -1;
-    }
-    absmax4_kernel<<<dim3(32, 4), 256, 0, c->stream>>>(aa, st.absmax_dev);
-    split_f16_tail_kernel<<<(unsigned)((g.N * 32 + 255) / 256), 256, 0, c->stream>>>(g.B2t, st.tail_hi, st.tail_lo, (int)g.N,
-                                                                                  (int)g.K2, st.absmax_dev + 3);
+  auto row_blocks = [](uint64_t rows) { return (unsigned)std::min<uint64_t>((rows + 7) / 8, 148 * 16); };
+  if (!reuse) {
+    const SplitJob ja{g.A, st.a_hi, st.a_lo, st.a_inv, (int)g.M, (int)g.K}, none{nullptr, nullptr, nullptr, nullptr, 0, 0};
+    split_rows_f16_kernel<<<row_blocks(g.M), 256, 0, c->stream>>>(ja, none);
+  }
+  if (g.K2) {       // the tail's A2 [M, K2] and B2 [N, K2] in one launch
+    const SplitJob j2{g.A2, st.a2_hi, st.a2_lo, st.a2_inv, (int)g.M, (int)g.K2};
+    const SplitJob jb{g.B2t, st.tail_hi, st.tail_lo, st.tail_inv, (int)g.N, (int)g.K2};
+    split_rows_f16_kernel<<<row_blocks(g.M + g.N), 256, 0, c->stream>>>(j2, jb);
   }
   F16pParams p{};
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.K2 = (int)g.K2;
   p.bias = g.bias; p.addend = g.addend; p.act = g.act; p.alpha = g.alpha == 0.0f ? 1.0f : g.alpha;
-  p.eb_pre = it->second.exp; p.inv_a = st.a_inv; p.inv_a2 = st.a2_inv; p.absmax = st.absmax_dev; p.err = st.err_dev;
+  p.eb_pre = it->second.exp; p.inv_a = st.a_inv; p.inv_a2 = st.a2_inv; p.inv_b2 = st.tail_inv; p.err = st.err_dev;
   p.n_tiles = (int)((g.N + 255) / 256);
   p.total_tiles = p.n_tiles * (int)(((g.M + BM - 1) / BM) / 2);
   cudaLaunchConfig_t cfg{};
@@ -2738,6 +2745,7 @@ void gemm_tensor_core_release(seeml_b200_ctx* c) {
   }
   cudaFree(sit->second.absmax_dev);
   cudaFree(sit->second.tail_hi);
+  cudaFree(sit->second.tail_inv);
   cudaFree(sit->second.a_hi); cudaFree(sit->second.a_lo); cudaFree(sit->second.a2_hi); cudaFree(sit->second.a2_lo);
   cudaFree(sit->second.a_inv); cudaFree(sit->second.a2_inv);
   states().erase(sit);
