@@ -222,7 +222,7 @@ def run_reference(args, cfg):
     if rank != 0:
         return
     model = build_model(cfg)
-    threads = os.cpu_count() or 1
+    threads = args.ref_threads or os.cpu_count() or 1
     base, ms = cpu_reference_sample(cfg, model, args.steps, args.warmup, threads)
     config = workload_config(args, cfg)
     config["reference_rows_timed_per_execution"] = base["rows_timed"]
@@ -669,6 +669,7 @@ def main():
     ap.add_argument("--config", default="c4", choices=sorted(CONFIGS) + ["c5"])
     ap.add_argument("--sweep-m", default="2048,16384,131072", help="row counts of the c5 sweep")
     ap.add_argument("--seeml-bench", default="", help="comma-separated fixtures (c1,c2,c3): print the seeml-bench shaped report")
+    ap.add_argument("--ref-threads", type=int, default=0, help="host threads of the reference arm (0 = all cores)")
     ap.add_argument("--steps-lo", type=int, default=20)
     ap.add_argument("--steps-hi", type=int, default=80)
     ap.add_argument("--gemm", default="f16x2", choices=sorted(GEMM_KINDS))

@@ -1315,7 +1315,7 @@ struct F16pParams {
   int eb_pre;                  // scale exponent of the frozen B copies
   const float* inv_a;          // [M]: 2^-e of each row of A (main pair)
   const float* inv_a2;         // [M]: the same for the tail's A2
-  const float* inv_b2;         // [N]: and for each row of the tail's B2 (an output column)
+  const float* inv_b2;         // [1]: and of the tail's B2 as a whole
   int n_tiles, total_tiles;
   int* err;
 };
@@ -1485,7 +1485,7 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
       tile_of(tl, m0, n0);
       const int m = m0 + row0 + lane;
       const float cs_main = (m < p.M ? p.inv_a[m] : 1.0f) * inv_b;
-      const float cs_tail = p.K2 && m < p.M ? p.inv_a2[m] : 1.0f;
+      const float cs_tail = p.K2 ? (m < p.M ? p.inv_a2[m] : 1.0f) * __ldg(p.inv_b2) : 1.0f;
 #pragma unroll
       for (int j = 0; j < NH; ++j) acc[j] = 0.0f;
       for (int ci = 0; ci < nchunks && ok; ++ci, ++cg) {
@@ -1493,20 +1493,14 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
         ok = mbar_wait(bar_acc_full(buf), (cg >> 1) & 1, p.err, 54);
         if (!ok) break;
         tc_fence_after();
+        const float cs = ci < nmain ? cs_main : cs_tail;
 #pragma unroll
         for (int c = 0; c < NH / LD; ++c) {
           uint32_t r[32];
           tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + buf * BN + half * NH + c * LD, r);
           tmem_ld_wait();
-          if (ci < nmain) {
 #pragma unroll
-            for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]) * cs_main;
-          } else {            // the tail's B2 is scaled per row of B2, i.e. per output column
-            const int col0 = n0 + half * NH + c * LD;
-#pragma unroll
-            for (int j = 0; j < LD; ++j)
-              acc[c * LD + j] += __uint_as_float(r[j]) * (cs_tail * (col0 + j < p.N ? __ldg(p.inv_b2 + col0 + j) : 1.0f));
-          }
+          for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]) * cs;
         }
         tc_fence_before();
         __syncwarp();
@@ -1580,6 +1574,181 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
   if (warp == 1) tmem_dealloc2(tmem_base, 512);
 }
 
+
+// ---------------------------------------- rank-r product on pre-split operands (F16X2)
+// out[M, BN] = alpha * A[M, K] . B[BN, K]^T for the LoRA factors (BN = 16 / 32 / 64), one CTA per
+// 128 rows, reading the fp16 hi / lo copies of A that the neighbouring frozen-weight GEMM uses
+// (split once by split_rows_f16_kernel) and a row-scaled split of the small factor. The kernel
+// only streams A: TMA -> tcgen05.mma kind::f16 -> chunked collection. B_hi and B_lo sit next to
+// each other in a stage, so one MMA of width 2 BN multiplies A_hi with [B_hi; B_lo] and a second
+// of width BN adds A_lo . B_hi: two instructions per 16 elements of K.
+struct RankF16Params {
+  int M, K;
+  float alpha;
+  const float* inv_a;      // [M]
+  const float* inv_b;      // [BN]
+  int* err;
+};
+template <int BN>
+struct RankF16Smem {
+  static constexpr int kA = kF16pTile, kB = BN * kF16pKB * 2;
+  static constexpr int kStage = 2 * kA + 2 * kB;                 // [A hi][A lo][B hi][B lo]
+  static constexpr int kStages = BN <= 32 ? 5 : 4;
+  static constexpr int kTotal = kStages * kStage + 256 + 1024;
+};
+constexpr int kRankThreads = 64 + 128;
+
+template <int BN>
+__global__ void __launch_bounds__(kRankThreads, 1)
+gemm_tc_rank_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
+                         const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo,
+                         const __grid_constant__ CUtensorMap mapC, RankF16Params p) {
+  using S = RankF16Smem<BN>;
+  constexpr int STAGES = S::kStages, KB = kF16pKB, CH = 2;
+  constexpr uint32_t kCols = 4 * BN < 32 ? 32 : 4 * BN;        // two accumulators of 2 BN columns
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + STAGES * S::kStage;
+  auto bar_full = [&](int s) { return bars + 8u * s; };
+  auto bar_empty = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto bar_acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto bar_acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (2 * STAGES + 4));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM;
+  const int nkb = (p.K + KB - 1) / KB;
+  const int nchunks = (nkb + CH - 1) / CH;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      int issued = 0;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % STAGES, r = kb / STAGES;
+        if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 61);
+        if (!ok) break;
+        const uint32_t stg = base + s * S::kStage;
+        mbar_expect_tx(bar_full(s), S::kStage);
+        tma_load_2d(stg, &mapAhi, bar_full(s), kb * KB, m0);
+        tma_load_2d(stg + S::kA, &mapAlo, bar_full(s), kb * KB, m0);
+        tma_load_2d(stg + 2 * S::kA, &mapBhi, bar_full(s), kb * KB, 0);
+        tma_load_2d(stg + 2 * S::kA + S::kB, &mapBlo, bar_full(s), kb * KB, 0);
+        ++issued;
+      }
+      if (!ok)
+        for (int kb = (issued > STAGES ? issued - STAGES : 0); kb < issued; ++kb)
+          mbar_wait(bar_full(kb % STAGES), (kb / STAGES) & 1, p.err, 65);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc1 = idesc_f16(BM, BN), idesc2 = idesc_f16(BM, 2 * BN);
+      bool ok = true;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES, r = kb / STAGES, ci = kb / CH, buf = ci & 1;
+        if (kb % CH == 0 && ci >= 2) {
+          ok = mbar_wait(bar_acc_empty(buf), ((ci >> 1) - 1) & 1, p.err, 66);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        ok = mbar_wait(bar_full(s), r & 1, p.err, 62);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * 2 * BN;
+        const uint32_t stg = base + s * S::kStage;
+#pragma unroll
+        for (int kk = 0; kk < KB / 16; ++kk) {
+          const uint64_t da = smem_desc_sw128(stg + kk * 32), dal = smem_desc_sw128(stg + S::kA + kk * 32);
+          const uint64_t db = smem_desc_sw128(stg + 2 * S::kA + kk * 32);      // B hi, with B lo right behind it
+          mma_f16(tmem_d, da, db, idesc2, ((kb % CH) | kk) != 0);
+          mma_f16(tmem_d, dal, db, idesc1, 1);
+        }
+        mma_commit(bar_empty(s));
+        if (kb % CH == CH - 1 || kb == nkb - 1) mma_commit(bar_acc_full(buf));
+      }
+    }
+  } else {
+    const int q = warp & 3, row0 = q * 32, m = m0 + row0 + lane;
+    const float cs_row = m < p.M ? p.inv_a[m] : 1.0f;
+    float acc[BN], csc[BN];
+#pragma unroll
+    for (int j = 0; j < BN; ++j) {
+      acc[j] = 0.0f;
+      csc[j] = cs_row * __ldg(p.inv_b + j);
+    }
+    bool ok = true;
+    for (int ci = 0; ci < nchunks && ok; ++ci) {
+      const int buf = ci & 1;
+      ok = mbar_wait(bar_acc_full(buf), (ci >> 1) & 1, p.err, 64);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < BN / 16; ++c) {
+        uint32_t rh[16], rl[16];
+        tmem_ld16(tmem_base + ((uint32_t)row0 << 16) + buf * 2 * BN + c * 16, rh);
+        tmem_ld16(tmem_base + ((uint32_t)row0 << 16) + buf * 2 * BN + BN + c * 16, rl);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[c * 16 + j] += (__uint_as_float(rh[j]) + __uint_as_float(rl[j])) * csc[c * 16 + j];
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty(buf));
+    }
+    if (ok && m0 + row0 < p.M) {
+      // every product has retired: stage 0 holds the store staging, one 32 x 32 box per warp, reused
+      uint8_t* stage_ptr = base_ptr + q * 4096;
+#pragma unroll
+      for (int c = 0; c < (BN + 31) / 32; ++c) {
+        if (c > 0) {
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+        }
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) {
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int col = c * 32 + j4 * 4 + e;
+            v[e] = col < BN ? p.alpha * acc[col < BN ? col : 0] : 0.0f;
+          }
+          *reinterpret_cast<float4*>(stage_ptr + lane * 128 + ((j4 ^ (lane & 7)) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&mapC, base + q * 4096, c * 32, m0 + row0);
+          tma_store_commit();
+        }
+      }
+      if (lane == 0) tma_store_wait_all();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kCols);
+}
+
 // One pass over a row-major f32 tensor [M, K]: each row's largest magnitude picks its power-of-two
 // scale 2^e (max * 2^e in [2^13, 2^14)), the row is cut into fp16 hi = fp16(x 2^e) and
 // lo = fp16(x 2^e - hi), and 2^-e goes to inv[row]. One warp per row; the second sweep over the
@@ -1612,10 +1781,45 @@ __device__ __forceinline__ void split_row_f16(const SplitJob& t, int row, int la
   }
   if (lane == 0) t.inv[row] = pow2i(-e);
 }
-__global__ void __launch_bounds__(256) split_rows_f16_kernel(SplitJob a, SplitJob b) {
+// whole != 0: tensor b is small and gets ONE scale (inv[0]); the last block handles all of it.
+__global__ void __launch_bounds__(256) split_rows_f16_kernel(SplitJob a, SplitJob b, int whole) {
   const int lane = threadIdx.x & 31;
-  const int total = a.M + b.M;
-  for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total; row += gridDim.x * 8) {
+  if (whole && blockIdx.x == gridDim.x - 1) {
+    __shared__ uint32_t smax[8];
+    const int n4 = (b.M * b.K) >> 2;
+    const float4* r4 = reinterpret_cast<const float4*>(b.src);
+    uint32_t mx = 0;
+    for (int i = threadIdx.x; i < n4; i += 256) {
+      const float4 v = r4[i];
+      mx = max(max(mx, __float_as_uint(v.x) & 0x7FFFFFFFu), max(max(__float_as_uint(v.y) & 0x7FFFFFFFu,
+               __float_as_uint(v.z) & 0x7FFFFFFFu), __float_as_uint(v.w) & 0x7FFFFFFFu));
+    }
+    mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+    if (lane == 0) smax[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = smax[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) mx = max(mx, smax[i]);
+    const int e = f16_scale_exp(mx);
+    const float sc = pow2i(e);
+    uint2* h2 = reinterpret_cast<uint2*>(b.hi);
+    uint2* l2 = reinterpret_cast<uint2*>(b.lo);
+    for (int i = threadIdx.x; i < n4; i += 256) {
+      const float4 v = r4[i];
+      float h0, h1, h2f, h3, l0, l1, l2f, l3;
+      split11(v.x * sc, h0, l0);
+      split11(v.y * sc, h1, l1);
+      split11(v.z * sc, h2f, l2f);
+      split11(v.w * sc, h3, l3);
+      h2[i] = make_uint2(pack_h2(h0, h1), pack_h2(h2f, h3));
+      l2[i] = make_uint2(pack_h2(l0, l1), pack_h2(l2f, l3));
+    }
+    if (threadIdx.x == 0) b.inv[0] = pow2i(-e);
+    return;
+  }
+  const int nb = whole ? (int)gridDim.x - 1 : (int)gridDim.x;
+  const int total = a.M + (whole ? 0 : b.M);
+  for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total; row += nb * 8) {
     if (row < a.M) split_row_f16(a, row, lane);
     else split_row_f16(b, row - a.M, lane);
   }
@@ -2040,6 +2244,7 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, u
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+constexpr uint64_t kRankKMax = 32768;       // longest reduction the rank-r F16X2 scratch holds
 constexpr uint64_t kF16TailRows = 65536;    // widest N the F16X2 tail scratch holds
 struct TcState {
   int* err_dev = nullptr;
@@ -2061,7 +2266,9 @@ struct TcState {
   const float* split_src = nullptr;             // the A operand a_hi / a_lo currently hold, and when it was split
   uint64_t split_m = 0, split_k = 0, split_unit = 0;
   __half *tail_hi = nullptr, *tail_lo = nullptr;
-  float* tail_inv = nullptr;                    // per-row 2^-e of the pre-split tail operand   // fp16 tiles of the low-rank tail's B operand, [kF16TailRows, 32] each
+  float* tail_inv = nullptr;                    // per-row 2^-e of the pre-split tail operand
+  __half *rank_b_hi = nullptr, *rank_b_lo = nullptr;   // pre-split LoRA factor of the rank-r kernel, [64, kRankKMax]
+  float* rank_b_inv = nullptr;   // fp16 tiles of the low-rank tail's B operand, [kF16TailRows, 32] each
   std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> maps;
   std::set<const void*> smem_attr_done;   // kernels whose dynamic shared-memory limit was raised on this context's device
 };
@@ -2276,6 +2483,28 @@ int launch_pair_f16(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   return 1;
 }
 
+// Makes a_hi / a_lo / a_inv hold the row-scaled fp16 split of A [M, K], unless the previous unit
+// of the same run already split this very tensor (q / k / v, gate / up, a LoRA factor product and
+// its GEMM): nothing has written it since. `extra` (optional) is a second, small tensor to split
+// row by row in the same launch.
+void split_a_rows(seeml_b200_ctx* c, TcState& st, const float* A, uint64_t M, uint64_t K, const SplitJob* extra = nullptr) {
+  const bool reuse = st.split_src == A && st.split_m == M && st.split_k == K &&
+                     (c->exec_unit == st.split_unit || c->exec_unit == st.split_unit + 1);
+  st.split_src = A; st.split_m = M; st.split_k = K; st.split_unit = c->exec_unit;
+  const SplitJob none{nullptr, nullptr, nullptr, nullptr, 0, 0};
+  if (reuse) {
+    if (extra) split_rows_f16_kernel<<<(unsigned)((extra->M + 7) / 8), 256, 0, c->stream>>>(*extra, none, 0);
+    return;
+  }
+  if (extra) {
+    const SplitJob ja2{A, st.a_hi, st.a_lo, st.a_inv, (int)M, (int)K};
+    split_rows_f16_kernel<<<(unsigned)std::min<uint64_t>((M + extra->M + 7) / 8, 148 * 16), 256, 0, c->stream>>>(ja2, *extra, 0);
+    return;
+  }
+  const SplitJob ja{A, st.a_hi, st.a_lo, st.a_inv, (int)M, (int)K};
+  split_rows_f16_kernel<<<(unsigned)std::min<uint64_t>((M + 7) / 8, 148 * 16), 256, 0, c->stream>>>(ja, none, 0);
+}
+
 // F16X2 with pre-split operands (see gemm_tc_pair_f16p_kernel). Needs the A scratch sized at build
 // time; anything it cannot take goes to launch_pair_f16.
 int launch_pair_f16p(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
@@ -2302,19 +2531,12 @@ int launch_pair_f16p(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   const CUtensorMap* mb2l = g.K2 ? cached_map_f16(st, st.tail_lo, g.N, g.K2, 128, true) : mbl;
   const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
   if (!mah || !mal || !ma2h || !ma2l || !mbh || !mbl || !mb2h || !mb2l || !mc) return -1;
-  // the previous unit of the same run split the same A (q / k / v, gate / up): nothing wrote it since
-  const bool reuse = st.split_src == g.A && st.split_m == g.M && st.split_k == g.K &&
-                     (c->exec_unit == st.split_unit || c->exec_unit == st.split_unit + 1);
-  st.split_src = g.A; st.split_m = g.M; st.split_k = g.K; st.split_unit = c->exec_unit;
+  split_a_rows(c, st, g.A, g.M, g.K);
   auto row_blocks = [](uint64_t rows) { return (unsigned)std::min<uint64_t>((rows + 7) / 8, 148 * 16); };
-  if (!reuse) {
-    const SplitJob ja{g.A, st.a_hi, st.a_lo, st.a_inv, (int)g.M, (int)g.K}, none{nullptr, nullptr, nullptr, nullptr, 0, 0};
-    split_rows_f16_kernel<<<row_blocks(g.M), 256, 0, c->stream>>>(ja, none);
-  }
   if (g.K2) {       // the tail's A2 [M, K2] and B2 [N, K2] in one launch
     const SplitJob j2{g.A2, st.a2_hi, st.a2_lo, st.a2_inv, (int)g.M, (int)g.K2};
     const SplitJob jb{g.B2t, st.tail_hi, st.tail_lo, st.tail_inv, (int)g.N, (int)g.K2};
-    split_rows_f16_kernel<<<row_blocks(g.M + g.N), 256, 0, c->stream>>>(j2, jb);
+    split_rows_f16_kernel<<<row_blocks(g.M) + 1, 256, 0, c->stream>>>(j2, jb, 1);     // B2 is small: one scale, last block
   }
   F16pParams p{};
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.K2 = (int)g.K2;
@@ -2446,6 +2668,37 @@ int gemm_tc_batched(seeml_b200_ctx* c, const TcBatched& g) {
   return 1;
 }
 
+namespace {
+// The rank-r product on the pre-split copies (F16X2). 1 = launched, 0 = not eligible.
+template <int BN>
+int launch_rank_f16p(seeml_b200_ctx* c, TcState& st, const float* A, const float* Bnk, float* out, uint64_t M,
+                     uint64_t K, float alpha) {
+  using S = RankF16Smem<BN>;
+  auto kern = gemm_tc_rank_f16p_kernel<BN>;
+  if (!ensure_smem_attr(st, kern, S::kTotal)) return -1;
+  if (!st.rank_b_hi) {
+    if (cudaMalloc(&st.rank_b_hi, 2 * 64 * kRankKMax * sizeof(__half)) != cudaSuccess ||
+        cudaMalloc(&st.rank_b_inv, 64 * sizeof(float)) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+    st.rank_b_lo = st.rank_b_hi + 64 * kRankKMax;
+  }
+  const CUtensorMap* mah = cached_map_f16(st, st.a_hi, M, K, BM, true);
+  const CUtensorMap* mal = cached_map_f16(st, st.a_lo, M, K, BM, true);
+  const CUtensorMap* mbh = cached_map_f16(st, st.rank_b_hi, BN, K, BN, true);
+  const CUtensorMap* mbl = cached_map_f16(st, st.rank_b_lo, BN, K, BN, true);
+  const CUtensorMap* mc = cached_map(st, out, M, BN, 32);
+  if (!mah || !mal || !mbh || !mbl || !mc) return -1;
+  const SplitJob jb{Bnk, st.rank_b_hi, st.rank_b_lo, st.rank_b_inv, BN, (int)K};
+  split_a_rows(c, st, A, M, K, &jb);
+  RankF16Params p{(int)M, (int)K, alpha, st.a_inv, st.rank_b_inv, st.err_dev};
+  kern<<<(unsigned)((M + BM - 1) / BM), kRankThreads, S::kTotal, c->stream>>>(*mah, *mal, *mbh, *mbl, *mc, p);
+  if (cudaGetLastError() != cudaSuccess) return -1;
+  return 1;
+}
+}  // namespace
+
 // ---- rank-r (LoRA factor) products on the tensor cores -------------------------------------
 // out[M,n] = alpha * A[M,K] . Bnk[n,K]^T for n in {16, 32, 64}: one CTA per 128 rows streams
 // A once through a deep TMA ring (HBM-bound). 1 = launched, 0 = not eligible.
@@ -2457,6 +2710,14 @@ int gemm_tc_rank_n(seeml_b200_ctx* c, const float* A, const float* Bnk, float* o
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bnk) | reinterpret_cast<uintptr_t>(out)) & 15) return 0;
   TcState* st = state_of(c, false);
   if (!st || !st->usable || !st->err_dev) return 0;
+  static const bool rank_f16 = [] { const char* e = std::getenv("SEEML_B200_F16_RANK"); return !e || std::atoi(e) != 0; }();
+  if (rank_f16 && c->gemm_kind == SEEML_B200_GEMM_F16X2 && K % 8 == 0 && K <= kRankKMax && M * K <= st->a_cap &&
+      M <= st->a_rows_cap && st->a_hi) {
+    int rr = n == 16 ? launch_rank_f16p<16>(c, *st, A, Bnk, out, M, K, alpha)
+                     : (n == 32 ? launch_rank_f16p<32>(c, *st, A, Bnk, out, M, K, alpha)
+                                : launch_rank_f16p<64>(c, *st, A, Bnk, out, M, K, alpha));
+    if (rr == 1) return 1;
+  }
   TcGemm g{};
   g.A = A; g.Bt = Bnk; g.C = out; g.M = M; g.N = n; g.K = K; g.alpha = alpha;
   const bool split = kind_x3(c);
@@ -2746,6 +3007,8 @@ void gemm_tensor_core_release(seeml_b200_ctx* c) {
   cudaFree(sit->second.absmax_dev);
   cudaFree(sit->second.tail_hi);
   cudaFree(sit->second.tail_inv);
+  cudaFree(sit->second.rank_b_hi);
+  cudaFree(sit->second.rank_b_inv);
   cudaFree(sit->second.a_hi); cudaFree(sit->second.a_lo); cudaFree(sit->second.a2_hi); cudaFree(sit->second.a2_lo);
   cudaFree(sit->second.a_inv); cudaFree(sit->second.a2_inv);
   states().erase(sit);
