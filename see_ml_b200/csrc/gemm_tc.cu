@@ -1304,7 +1304,8 @@ constexpr int kF16pTile = BM * kF16pKB * 2;       // 16 KiB: 128 rows x 64 fp16
 struct PairF16pSmem {
   static constexpr int kAHi = 0, kALo = kF16pTile, kBHi = 2 * kF16pTile, kBLo = 3 * kF16pTile;
   static constexpr int kStage = 4 * kF16pTile;    // 64 KiB
-  static constexpr int kTotal = kF16pStages * kStage + 256 + 1024;
+  static constexpr int kEpi = (kWorkers / 32) * 4096;           // store staging of its own: one 32 x 32 box per worker warp
+  static constexpr int kTotal = kF16pStages * kStage + kEpi + 256 + 1024;
 };
 struct F16pParams {
   int M, N, K, K2;
@@ -1331,7 +1332,7 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t bars = base + STAGES * S::kStage;
+  const uint32_t bars = base + STAGES * S::kStage + S::kEpi;
   auto bar_full = [&](int s) { return bars + 8u * s; };
   auto bar_peer = [&](int s) { return bars + 8u * (STAGES + s); };        // even CTA: the odd CTA's stage has landed
   auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
@@ -1340,7 +1341,7 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
   const uint32_t bar_epi = bars + 8u * (3 * STAGES + 4);
   const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 5);
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + 8 * (3 * STAGES + 5));
+      reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + S::kEpi + 8 * (3 * STAGES + 5));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -1384,19 +1385,15 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
   if (warp == 0) {
     // ---- TMA producer: four fp16 tiles per stage ------------------------------------------------
     if (lane == 0) {
-      int it = 0, ti = 0, pend = -1, epi_stage = -1;
+      int it = 0;
       bool ok = true;
-      for (int tl = cid; tl < p.total_tiles && ok; tl += ncl, ++ti) {
+      for (int tl = cid; tl < p.total_tiles && ok; tl += ncl) {
         int m0, n0;
         tile_of(tl, m0, n0);
         const int nb = n0 + (int)rank * 128;
         for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
           const int s = it % STAGES, r = it / STAGES;
           if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 51);
-          if (ok && pend >= 0 && s == epi_stage) {
-            ok = mbar_wait(bar_epi, pend & 1, p.err, 58);
-            pend = -1;
-          }
           if (!ok) break;
           const uint32_t stg = base + s * S::kStage;
           mbar_expect_tx(bar_full(s), 4 * kF16pTile);
@@ -1412,12 +1409,6 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
             tma_load_2d(stg + S::kBLo, &mapB2lo, bar_full(s), (kb - nkb1) * KB, nb);
           }
         }
-        if (ok && pend >= 0) {
-          ok = mbar_wait(bar_epi, pend & 1, p.err, 58);
-          pend = -1;
-        }
-        pend = ti;
-        epi_stage = (it - 1) % STAGES;
       }
       if (!ok) {
         for (int kb = (it > STAGES ? it - STAGES : 0); kb < it; ++kb)
@@ -1507,9 +1498,8 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
         if (lane == 0) mbar_arrive_remote(bar_acc_empty(buf), 0);
       }
       if (!ok) break;
-      // the stage of the tile's last k-block is the one the producer refills last: store staging
-      const int it_last = (tiles_done + 1) * nkb - 1;
-      const uint32_t box = (uint32_t)((it_last % STAGES) * S::kStage + (warp - 2) * 4096);
+      // store staging lives behind the stage ring, so the loads of the next tile never wait for it
+      const uint32_t box = (uint32_t)(STAGES * S::kStage + (warp - 2) * 4096);
       if (m0 + row0 < p.M) {
         bool stored = false;
 #pragma unroll
@@ -1517,7 +1507,7 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
           const int ncol = n0 + half * NH + c * LD;
           if (ncol < p.N) {
             uint8_t* stage_ptr = base_ptr + box;
-            if (stored) {
+            if (stored || tiles_done > 0) {          // the box's previous store (this tile's or the last tile's) has been read
               if (lane == 0) tma_store_wait_read();
               __syncwarp();
             }
@@ -1560,11 +1550,6 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
           }
         }
       }
-      if (lane == 0) {
-        tma_store_wait_read();
-        mbar_arrive(bar_epi);
-      }
-      __syncwarp();
     }
     if (lane == 0) tma_store_wait_all();
   }
@@ -1781,14 +1766,49 @@ __device__ __forceinline__ void split_row_f16(const SplitJob& t, int row, int la
   }
   if (lane == 0) t.inv[row] = pow2i(-e);
 }
-// whole != 0: tensor b is small and gets ONE scale (inv[0]); the last block handles all of it.
+// The row of NV * 128 floats held in registers between the maximum and the conversion: one read.
+template <int NV>
+__device__ __forceinline__ void split_row_f16_regs(const SplitJob& t, int row, int lane) {
+  const float4* r4 = reinterpret_cast<const float4*>(t.src + (size_t)row * t.K);
+  float4 v[NV];
+  uint32_t mx = 0;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) v[i] = r4[lane + 32 * i];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+    mx = max(max(mx, __float_as_uint(v[i].x) & 0x7FFFFFFFu), max(max(__float_as_uint(v[i].y) & 0x7FFFFFFFu,
+             __float_as_uint(v[i].z) & 0x7FFFFFFFu), __float_as_uint(v[i].w) & 0x7FFFFFFFu));
+  mx = __reduce_max_sync(0xFFFFFFFFu, mx);
+  const int e = f16_scale_exp(mx);
+  const float sc = pow2i(e);
+  uint2* h2 = reinterpret_cast<uint2*>(t.hi + (size_t)row * t.K);
+  uint2* l2 = reinterpret_cast<uint2*>(t.lo + (size_t)row * t.K);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float h0, h1, h2f, h3, l0, l1, l2f, l3;
+    split11(v[i].x * sc, h0, l0);
+    split11(v[i].y * sc, h1, l1);
+    split11(v[i].z * sc, h2f, l2f);
+    split11(v[i].w * sc, h3, l3);
+    h2[lane + 32 * i] = make_uint2(pack_h2(h0, h1), pack_h2(h2f, h3));
+    l2[lane + 32 * i] = make_uint2(pack_h2(l0, l1), pack_h2(l2f, l3));
+  }
+  if (lane == 0) t.inv[row] = pow2i(-e);
+}
+
+// whole != 0: tensor b is small and gets ONE scale (inv[0]); the last kWholeBlocks blocks share it,
+// each finding the maximum of all of b on its own (b is a few hundred KB in L2) and converting a slice.
+constexpr int kWholeBlocks = 16;
+template <int NV>
 __global__ void __launch_bounds__(256) split_rows_f16_kernel(SplitJob a, SplitJob b, int whole) {
   const int lane = threadIdx.x & 31;
-  if (whole && blockIdx.x == gridDim.x - 1) {
+  const int nb = whole ? (int)gridDim.x - kWholeBlocks : (int)gridDim.x;
+  if (whole && (int)blockIdx.x >= nb) {
     __shared__ uint32_t smax[8];
     const int n4 = (b.M * b.K) >> 2;
     const float4* r4 = reinterpret_cast<const float4*>(b.src);
     uint32_t mx = 0;
+#pragma unroll 8
     for (int i = threadIdx.x; i < n4; i += 256) {
       const float4 v = r4[i];
       mx = max(max(mx, __float_as_uint(v.x) & 0x7FFFFFFFu), max(max(__float_as_uint(v.y) & 0x7FFFFFFFu,
@@ -1804,7 +1824,9 @@ __global__ void __launch_bounds__(256) split_rows_f16_kernel(SplitJob a, SplitJo
     const float sc = pow2i(e);
     uint2* h2 = reinterpret_cast<uint2*>(b.hi);
     uint2* l2 = reinterpret_cast<uint2*>(b.lo);
-    for (int i = threadIdx.x; i < n4; i += 256) {
+    const int part = (int)blockIdx.x - nb;
+#pragma unroll 4
+    for (int i = part * 256 + threadIdx.x; i < n4; i += kWholeBlocks * 256) {
       const float4 v = r4[i];
       float h0, h1, h2f, h3, l0, l1, l2f, l3;
       split11(v.x * sc, h0, l0);
@@ -1814,15 +1836,26 @@ __global__ void __launch_bounds__(256) split_rows_f16_kernel(SplitJob a, SplitJo
       h2[i] = make_uint2(pack_h2(h0, h1), pack_h2(h2f, h3));
       l2[i] = make_uint2(pack_h2(l0, l1), pack_h2(l2f, l3));
     }
-    if (threadIdx.x == 0) b.inv[0] = pow2i(-e);
+    if (part == 0 && threadIdx.x == 0) b.inv[0] = pow2i(-e);
     return;
   }
-  const int nb = whole ? (int)gridDim.x - 1 : (int)gridDim.x;
   const int total = a.M + (whole ? 0 : b.M);
   for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < total; row += nb * 8) {
-    if (row < a.M) split_row_f16(a, row, lane);
-    else split_row_f16(b, row - a.M, lane);
+    if (row < a.M) {
+      if constexpr (NV > 0) split_row_f16_regs<NV>(a, row, lane);
+      else split_row_f16(a, row, lane);
+    } else {
+      split_row_f16(b, row - a.M, lane);
+    }
   }
+}
+// NV = a.K / 128 when the first tensor's rows fit the register variant, else 0
+inline void launch_split_rows(unsigned blocks, cudaStream_t st, const SplitJob& a, const SplitJob& b, int whole) {
+  const int nv = (a.K % 128 == 0) ? a.K / 128 : 0;
+  if (nv == 8) split_rows_f16_kernel<8><<<blocks, 256, 0, st>>>(a, b, whole);
+  else if (nv == 22) split_rows_f16_kernel<22><<<blocks, 256, 0, st>>>(a, b, whole);
+  else if (nv == 32) split_rows_f16_kernel<32><<<blocks, 256, 0, st>>>(a, b, whole);
+  else split_rows_f16_kernel<0><<<blocks, 256, 0, st>>>(a, b, whole);
 }
 
 // max|x| (as f32 bit patterns, which order like the magnitudes; a NaN sorts above every finite
@@ -2493,16 +2526,16 @@ void split_a_rows(seeml_b200_ctx* c, TcState& st, const float* A, uint64_t M, ui
   st.split_src = A; st.split_m = M; st.split_k = K; st.split_unit = c->exec_unit;
   const SplitJob none{nullptr, nullptr, nullptr, nullptr, 0, 0};
   if (reuse) {
-    if (extra) split_rows_f16_kernel<<<(unsigned)((extra->M + 7) / 8), 256, 0, c->stream>>>(*extra, none, 0);
+    if (extra) launch_split_rows((unsigned)((extra->M + 7) / 8), c->stream, *extra, none, 0);
     return;
   }
   if (extra) {
     const SplitJob ja2{A, st.a_hi, st.a_lo, st.a_inv, (int)M, (int)K};
-    split_rows_f16_kernel<<<(unsigned)std::min<uint64_t>((M + extra->M + 7) / 8, 148 * 16), 256, 0, c->stream>>>(ja2, *extra, 0);
+    launch_split_rows((unsigned)std::min<uint64_t>((M + extra->M + 7) / 8, 148 * 16), c->stream, ja2, *extra, 0);
     return;
   }
   const SplitJob ja{A, st.a_hi, st.a_lo, st.a_inv, (int)M, (int)K};
-  split_rows_f16_kernel<<<(unsigned)std::min<uint64_t>((M + 7) / 8, 148 * 16), 256, 0, c->stream>>>(ja, none, 0);
+  launch_split_rows((unsigned)std::min<uint64_t>((M + 7) / 8, 148 * 16), c->stream, ja, none, 0);
 }
 
 // F16X2 with pre-split operands (see gemm_tc_pair_f16p_kernel). Needs the A scratch sized at build
@@ -2536,7 +2569,7 @@ int launch_pair_f16p(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   if (g.K2) {       // the tail's A2 [M, K2] and B2 [N, K2] in one launch
     const SplitJob j2{g.A2, st.a2_hi, st.a2_lo, st.a2_inv, (int)g.M, (int)g.K2};
     const SplitJob jb{g.B2t, st.tail_hi, st.tail_lo, st.tail_inv, (int)g.N, (int)g.K2};
-    split_rows_f16_kernel<<<row_blocks(g.M) + 1, 256, 0, c->stream>>>(j2, jb, 1);     // B2 is small: one scale, last block
+    launch_split_rows(row_blocks(g.M) + kWholeBlocks, c->stream, j2, jb, 1);     // B2 is small: one scale, the last blocks
   }
   F16pParams p{};
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.K2 = (int)g.K2;
