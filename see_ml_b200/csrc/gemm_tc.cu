@@ -1318,6 +1318,7 @@ struct F16pParams {
   const float* inv_a2;         // [M]: the same for the tail's A2
   const float* inv_b2;         // [1]: and of the tail's B2 as a whole
   int n_tiles, total_tiles;
+  int full_tiles;              // tiles [0, full_tiles) are 256 columns wide; the rest are halves of the leftover tiles
   int* err;
 };
 
@@ -1326,6 +1327,8 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
                          const __grid_constant__ CUtensorMap mapA2hi, const __grid_constant__ CUtensorMap mapA2lo,
                          const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo,
                          const __grid_constant__ CUtensorMap mapB2hi, const __grid_constant__ CUtensorMap mapB2lo,
+                         const __grid_constant__ CUtensorMap mapBhiH, const __grid_constant__ CUtensorMap mapBloH,
+                         const __grid_constant__ CUtensorMap mapB2hiH, const __grid_constant__ CUtensorMap mapB2loH,
                          const __grid_constant__ CUtensorMap mapC, F16pParams p) {
   using S = PairF16pSmem;
   constexpr int STAGES = kF16pStages, BN = 256, KB = kF16pKB, CH = 2;   // CH k-blocks (128 elements of K) per chunk
@@ -1346,9 +1349,20 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int cid = (int)(blockIdx.x >> 1), ncl = (int)(gridDim.x >> 1);
-  auto tile_of = [&](int t, int& m0, int& n0) {
-    n0 = (t % p.n_tiles) * BN;
-    m0 = (2 * (t / p.n_tiles) + (int)rank) * BM;
+  // The tiles of the last, partly filled wave are cut into two 128-column halves (the *H maps load
+  // 64-row B boxes), so that wave costs half a tile time instead of a whole one.
+  auto tile_of = [&](int t, int& m0, int& n0, int& bn) {
+    int full = t;
+    bn = BN;
+    int shift = 0;
+    if (t >= p.full_tiles) {
+      const int h = t - p.full_tiles;
+      full = p.full_tiles + (h >> 1);
+      bn = BN / 2;
+      shift = (h & 1) * (BN / 2);
+    }
+    n0 = (full % p.n_tiles) * BN + shift;
+    m0 = (2 * (full / p.n_tiles) + (int)rank) * BM;
   };
   const int nkb1 = (p.K + KB - 1) / KB;
   const int nkb = nkb1 + (p.K2 + KB - 1) / KB;
@@ -1388,25 +1402,26 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
       int it = 0;
       bool ok = true;
       for (int tl = cid; tl < p.total_tiles && ok; tl += ncl) {
-        int m0, n0;
-        tile_of(tl, m0, n0);
-        const int nb = n0 + (int)rank * 128;
+        int m0, n0, bn;
+        tile_of(tl, m0, n0, bn);
+        const int nb = n0 + (int)rank * (bn / 2);
+        const bool wide = bn == BN;
         for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
           const int s = it % STAGES, r = it / STAGES;
           if (r > 0) ok = mbar_wait(bar_empty(s), (r - 1) & 1, p.err, 51);
           if (!ok) break;
           const uint32_t stg = base + s * S::kStage;
-          mbar_expect_tx(bar_full(s), 4 * kF16pTile);
+          mbar_expect_tx(bar_full(s), 2 * kF16pTile + 2 * (bn / 2) * kF16pKB * 2);
           if (kb < nkb1) {
             tma_load_2d(stg + S::kAHi, &mapAhi, bar_full(s), kb * KB, m0);
             tma_load_2d(stg + S::kALo, &mapAlo, bar_full(s), kb * KB, m0);
-            tma_load_2d(stg + S::kBHi, &mapBhi, bar_full(s), kb * KB, nb);
-            tma_load_2d(stg + S::kBLo, &mapBlo, bar_full(s), kb * KB, nb);
+            tma_load_2d(stg + S::kBHi, wide ? &mapBhi : &mapBhiH, bar_full(s), kb * KB, nb);
+            tma_load_2d(stg + S::kBLo, wide ? &mapBlo : &mapBloH, bar_full(s), kb * KB, nb);
           } else {
             tma_load_2d(stg + S::kAHi, &mapA2hi, bar_full(s), (kb - nkb1) * KB, m0);
             tma_load_2d(stg + S::kALo, &mapA2lo, bar_full(s), (kb - nkb1) * KB, m0);
-            tma_load_2d(stg + S::kBHi, &mapB2hi, bar_full(s), (kb - nkb1) * KB, nb);
-            tma_load_2d(stg + S::kBLo, &mapB2lo, bar_full(s), (kb - nkb1) * KB, nb);
+            tma_load_2d(stg + S::kBHi, wide ? &mapB2hi : &mapB2hiH, bar_full(s), (kb - nkb1) * KB, nb);
+            tma_load_2d(stg + S::kBLo, wide ? &mapB2lo : &mapB2loH, bar_full(s), (kb - nkb1) * KB, nb);
           }
         }
       }
@@ -1428,10 +1443,10 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
         }
     } else if (lane == 0) {
       // ---- even CTA: MMA issuer ---------------------------------------------------------------
-      constexpr uint32_t idesc = idesc_f16(256, BN);
       bool ok = true;
       int it = 0, ci = 0;
-      for (int tl = cid; tl < p.total_tiles && ok; tl += ncl)
+      for (int tl = cid; tl < p.total_tiles && ok; tl += ncl) {
+      const uint32_t idesc = tl < p.full_tiles ? idesc_f16(256, BN) : idesc_f16(256, BN / 2);
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = it % STAGES, r = it / STAGES;
         const int buf = ci & 1;
@@ -1462,6 +1477,7 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
           ++ci;
         }
       }
+      }
     }
   } else {
     // ---- worker warps (both CTAs): collect finished chunks, epilogue ----------------------------
@@ -1472,8 +1488,9 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
     bool ok = true;
     int cg = 0, tiles_done = 0;
     for (int tl = cid; tl < p.total_tiles && ok; tl += ncl, ++tiles_done) {
-      int m0, n0;
-      tile_of(tl, m0, n0);
+      int m0, n0, bn;
+      tile_of(tl, m0, n0, bn);
+      const int nh = bn / 2, boxes = nh / LD;      // this warp's share of the tile's columns
       const int m = m0 + row0 + lane;
       const float cs_main = (m < p.M ? p.inv_a[m] : 1.0f) * inv_b;
       const float cs_tail = p.K2 ? (m < p.M ? p.inv_a2[m] : 1.0f) * __ldg(p.inv_b2) : 1.0f;
@@ -1487,11 +1504,13 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
         const float cs = ci < nmain ? cs_main : cs_tail;
 #pragma unroll
         for (int c = 0; c < NH / LD; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + buf * BN + half * NH + c * LD, r);
-          tmem_ld_wait();
+          if (c < boxes) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)row0 << 16) + buf * BN + half * nh + c * LD, r);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]) * cs;
+            for (int j = 0; j < LD; ++j) acc[c * LD + j] += __uint_as_float(r[j]) * cs;
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -1504,8 +1523,8 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
         bool stored = false;
 #pragma unroll
         for (int c = 0; c < NH / LD; ++c) {
-          const int ncol = n0 + half * NH + c * LD;
-          if (ncol < p.N) {
+          const int ncol = n0 + half * nh + c * LD;
+          if (c < boxes && ncol < p.N) {
             uint8_t* stage_ptr = base_ptr + box;
             if (stored || tiles_done > 0) {          // the box's previous store (this tile's or the last tile's) has been read
               if (lane == 0) tma_store_wait_read();
@@ -2563,7 +2582,11 @@ int launch_pair_f16p(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   const CUtensorMap* mb2h = g.K2 ? cached_map_f16(st, st.tail_hi, g.N, g.K2, 128, true) : mbh;
   const CUtensorMap* mb2l = g.K2 ? cached_map_f16(st, st.tail_lo, g.N, g.K2, 128, true) : mbl;
   const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
-  if (!mah || !mal || !ma2h || !ma2l || !mbh || !mbl || !mb2h || !mb2l || !mc) return -1;
+  const CUtensorMap* mbhH = cached_map_f16(st, it->second.hi, g.N, g.K, 64, true);      // 64-row boxes for half tiles
+  const CUtensorMap* mblH = cached_map_f16(st, it->second.lo, g.N, g.K, 64, true);
+  const CUtensorMap* mb2hH = g.K2 ? cached_map_f16(st, st.tail_hi, g.N, g.K2, 64, true) : mbhH;
+  const CUtensorMap* mb2lH = g.K2 ? cached_map_f16(st, st.tail_lo, g.N, g.K2, 64, true) : mblH;
+  if (!mah || !mal || !ma2h || !ma2l || !mbh || !mbl || !mb2h || !mb2l || !mc || !mbhH || !mblH || !mb2hH || !mb2lH) return -1;
   split_a_rows(c, st, g.A, g.M, g.K);
   auto row_blocks = [](uint64_t rows) { return (unsigned)std::min<uint64_t>((rows + 7) / 8, 148 * 16); };
   if (g.K2) {       // the tail's A2 [M, K2] and B2 [N, K2] in one launch
@@ -2595,9 +2618,20 @@ int launch_pair_f16p(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
     }
     st.pair_f16p_clusters = n;
   }
+  // a partly filled last wave: its tiles are cut in two when the halves still fit one wave
+  p.full_tiles = p.total_tiles;
+  static const bool halves = [] { const char* e = std::getenv("SEEML_B200_F16_HALF_TILES"); return !e || std::atoi(e) != 0; }();
+  const int ncl = st.pair_f16p_clusters;
+  if (halves && p.total_tiles > ncl) {
+    const int left = p.total_tiles % ncl;
+    if (left > 0 && 2 * left <= ncl) {
+      p.full_tiles = p.total_tiles - left;
+      p.total_tiles = p.full_tiles + 2 * left;
+    }
+  }
   cfg.gridDim = dim3(2u * (unsigned)std::min(p.total_tiles, st.pair_f16p_clusters));
   const cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_pair_f16p_kernel, *mah, *mal, *ma2h, *ma2l, *mbh, *mbl, *mb2h,
-                                            *mb2l, *mc, p);
+                                            *mb2l, *mbhH, *mblH, *mb2hH, *mb2lH, *mc, p);
   if (le != cudaSuccess) {
     cudaGetLastError();
     return -1;

@@ -92,7 +92,7 @@ int swiglu_bwd(const float* dm, const float* u, const float* s, const float* g, 
 // loss, (probs when not null) and dlogits = (seed / N) (p - onehot) in one pass; scratch as xent_fwd
 int xent_fused(const float* logits, const int32_t* labels, float* loss, float* probs, float* dlogits, float seed,
                size_t N, size_t C, double* scratch, cudaStream_t st);
-struct AdamwDesc { float* p; const float* g; float* m; float* v; uint64_t n; uint32_t first_block; uint32_t pad; };
+struct AdamwDesc { float* p; const float* g; float* m; float* v; uint64_t n; uint32_t first_block; uint32_t pad; };   // pad: 1 = 128-bit accesses allowed
 int adamw_multi(const AdamwDesc* descs_dev, int ndesc, unsigned total_blocks, const DevScalars* sc, cudaStream_t st);
 
 struct Span { uint64_t arena_off; uint64_t count; uint64_t packed_off; };

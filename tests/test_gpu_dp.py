@@ -86,3 +86,38 @@ def test_k_chunk_step_matches_oracle_chunks_tree_and_optimizer(mode):
     # and the whole step is bit-reproducible run to run
     assert runs[1][0] == loss
     np.testing.assert_array_equal(runs[1][2], got_p)
+
+
+def test_collective_wait_has_a_deadline_and_aborts_the_communicator():
+    """Failure detection without a GPU fault: the host-side wait on the exchange polls the
+    communicator and the stream; when the stream does not drain before the deadline (here: a
+    bounded one-second device sleep stands in for a rank that never posts) the call returns an
+    attributable error and aborts the communicator instead of blocking. The context stays usable."""
+    import ctypes as C
+    import torch
+    lib = L.lib()
+    raw = (C.c_uint8 * 128)()
+    L.check(lib.seeml_b200_comm_unique_id(raw))
+    comm = C.c_void_p()
+    L.check(lib.seeml_b200_comm_init(0, raw, 0, 1, C.byref(comm)))
+    from see_ml_b200.engine import Context
+    ctx = Context(1 << 20)
+    stream = torch.cuda.ExternalStream(lib.seeml_b200_ctx_stream(ctx.h), device=torch.device("cuda", 0))
+    # a healthy exchange first: world 1 all-gather of 256 floats, waited for with a generous deadline
+    base = lib.seeml_b200_ctx_arena(ctx.h)
+    ctx.write(0, np.arange(256, dtype=np.float32))
+    L.check(lib.seeml_b200_comm_allgather(comm, C.c_void_p(base), C.c_void_p(base + 4096), 256,
+                                          C.c_void_p(lib.seeml_b200_ctx_stream(ctx.h))))
+    L.check(lib.seeml_b200_comm_wait(comm, C.c_void_p(lib.seeml_b200_ctx_stream(ctx.h)), 30.0))
+    np.testing.assert_array_equal(ctx.read(4096, 1024).view(np.float32), np.arange(256, dtype=np.float32))
+    with torch.cuda.stream(stream):
+        torch.cuda._sleep(int(2.0e9))            # about a second of bounded device time
+    rc = lib.seeml_b200_comm_wait(comm, C.c_void_p(lib.seeml_b200_ctx_stream(ctx.h)), 0.05)
+    assert rc != 0 and "did not finish within" in L.last_error() and L.last_error().startswith("UpdateEngine: ")
+    assert lib.seeml_b200_comm_allgather(comm, C.c_void_p(base), C.c_void_p(base + 4096), 256,
+                                         C.c_void_p(lib.seeml_b200_ctx_stream(ctx.h))) != 0
+    assert "aborted" in L.last_error()
+    torch.cuda.synchronize()
+    ctx.write(0, np.ones(4, np.float32))         # the context still works
+    lib.seeml_b200_comm_destroy(comm)
+    ctx.close()

@@ -186,3 +186,25 @@ def test_dataset_file_round_trip_and_rejections(backend_lib, tmp_path):
         Dataset.from_tokens(np.array([[1, -2, 3]], np.int32))
     with pytest.raises(L.BackendError, match="validation fraction"):
         d.split_validation(1.5)
+
+
+def test_data_parallel_entry_points_refuse_bad_arguments_with_attributable_errors(backend_lib):
+    """The communicator layer binds NCCL at run time and never aborts: a rank outside the world,
+    a missing id, a step on an engine that was never configured - each is an error string with
+    a registered unit, with or without a GPU in the machine."""
+    import ctypes as C
+    lib = backend_lib
+    raw = (C.c_uint8 * 128)()
+    out = C.c_void_p()
+    assert lib.seeml_b200_comm_init(0, raw, 3, 2, C.byref(out)) != 0
+    assert L.last_error().startswith("UpdateEngine: rank / world size out of range")
+    assert lib.seeml_b200_comm_init(0, None, 0, 1, C.byref(out)) != 0
+    assert L.last_error().startswith("UpdateEngine: ")
+    assert lib.seeml_b200_comm_unique_id(None) != 0 and L.last_error().startswith("UpdateEngine: ")
+    assert lib.seeml_b200_engine_dp_configure(None, 8, 0, 1, None) != 0
+    assert L.last_error() == "UpdateEngine: no plan loaded"
+    loss = C.c_float()
+    assert lib.seeml_b200_engine_dp_step_host(None, raw, raw, C.byref(loss)) != 0
+    assert "not configured" in L.last_error()
+    assert lib.seeml_b200_comm_rank(None) == 0 and lib.seeml_b200_comm_world(None) == 1
+    lib.seeml_b200_comm_destroy(None)
