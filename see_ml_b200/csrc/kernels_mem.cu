@@ -898,72 +898,6 @@ __global__ void __launch_bounds__(kThreads) adamw_multi_kernel(const AdamwDesc* 
   }
 }
 
-// The same single pass with the row parked in shared memory (one block of 1024 threads per row, C
-// floats of dynamic shared memory): the logits are read from memory once and the gradient written
-// once. For wide rows (a 32000-word vocabulary is 125 KB).
-__global__ void __launch_bounds__(1024) xent_fused_smem_kernel(
-    const float* logits, const int32_t* __restrict__ labels, float* probs, float* d,
-    double* __restrict__ terms, size_t N, size_t C, float scale) {
-  extern __shared__ float4 row4[];
-  __shared__ double smd[32];
-  __shared__ float smf[32];
-  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
-  const size_t C4 = C >> 2;
-  for (size_t n = blockIdx.x; n < N; n += gridDim.x) {
-    const float4* z4 = reinterpret_cast<const float4*>(logits + n * C);
-    float mx = -INFINITY;
-#pragma unroll 8
-    for (size_t c = tid; c < C4; c += 1024) {
-      const float4 v = z4[c];
-      row4[c] = v;
-      mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
-    }
-    mx = warp_max(mx);
-    if (lane == 0) smf[w] = mx;
-    __syncthreads();
-    mx = smf[0];
-#pragma unroll
-    for (int i = 1; i < 32; ++i) mx = fmaxf(mx, smf[i]);
-    double sum = 0.0;
-    for (size_t c = tid; c < C4; c += 1024) {
-      const float4 v = row4[c];
-      float4 ev;
-      ev.x = expf(v.x - mx); ev.y = expf(v.y - mx); ev.z = expf(v.z - mx); ev.w = expf(v.w - mx);
-      row4[c] = ev;
-      sum += ev.x; sum += ev.y; sum += ev.z; sum += ev.w;
-    }
-    sum = warp_sum(sum);
-    if (lane == 0) smd[w] = sum;
-    __syncthreads();
-    double tot = 0.0;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) tot += smd[i];
-    const float inv = 1.0f / (float)tot;
-    const uint32_t lab = (uint32_t)labels[n];
-    if (tid == 0) {
-      const float pl = lab < C ? reinterpret_cast<const float*>(row4)[lab] * inv : __int_as_float(0x7fc00000);
-      const double safe = isnan(pl) ? (double)pl : (double)fmaxf(pl, 1e-12f);
-      terms[n] = -log(safe);
-    }
-    for (size_t c = tid; c < C4; c += 1024) {
-      float4 pv = row4[c];
-      pv.x *= inv; pv.y *= inv; pv.z *= inv; pv.w *= inv;
-      if (probs != nullptr) reinterpret_cast<float4*>(probs + n * C)[c] = pv;
-      float4 v;
-      v.x = scale * pv.x; v.y = scale * pv.y; v.z = scale * pv.z; v.w = scale * pv.w;
-      const size_t k = (size_t)lab - 4 * c;
-      if (k < 4) {
-        if (k == 0) v.x -= scale;
-        else if (k == 1) v.y -= scale;
-        else if (k == 2) v.z -= scale;
-        else v.w -= scale;
-      }
-      reinterpret_cast<float4*>(d + n * C)[c] = v;
-    }
-    __syncthreads();        // the row buffer and the reduction slots are reused by the next row
-  }
-}
-
 // ---- gate metrics ---------------------------------------------------------------------------
 // Exact argmax accuracy: the first column holding the row maximum wins, as the
 // reference's strict '>' scan does. One warp per row; integer atomics only.
@@ -1273,18 +1207,6 @@ int xent_fused(const float* logits, const int32_t* labels, float* loss, float* p
   if (N == 0) return 0;
   const float scale = seed / (float)N;
   const int vec = C % 4 == 0 && aligned16(logits) && aligned16(dlogits) && (probs == nullptr || aligned16(probs));
-  if (vec && C >= 8192 && C * 4 <= 200 * 1024) {
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-      cudaFuncSetAttribute(xent_fused_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-      attr_set[dev] = true;
-    }
-    xent_fused_smem_kernel<<<grid_for(N, 1, 1), 1024, C * 4, st>>>(logits, labels, probs, dlogits, scratch, N, C, scale);
-    if (cudaGetLastError() == cudaSuccess)
-      return 1 + finish_loss(scratch, N, chunk_grain(N, row_grain(C, 4096)), (double)N, loss, st);
-  }
   if (C <= 1024)
     xent_fused_rows_kernel<32><<<grid_for(N, kThreads / 32, 16), kThreads, 0, st>>>(logits, labels, probs, dlogits,
                                                                                    scratch, N, C, scale, vec);

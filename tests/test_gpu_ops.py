@@ -203,3 +203,57 @@ def test_elementwise_fused_groups_are_bit_identical_to_the_instruction_path():
         ctx.close()
     np.testing.assert_array_equal(outs[MODE_FUSED][0], outs[MODE_CONTRACT][0])
     assert outs[MODE_FUSED][1] <= outs[MODE_CONTRACT][1] - 8, outs[MODE_FUSED][1:] + outs[MODE_CONTRACT][1:]
+
+
+def test_fused_lora_backward_with_result_over_dt_and_da_over_the_addend():
+    """A slot layout the planner may produce: the group's result is planned over dt (whose last
+    reader, dA, precedes the final add in the stream) while dA itself is planned over the addend
+    (dead after the first add). Fused, dA runs after the GEMM, so the result must wait in a
+    temporary until dA has read dt. Fused and per-instruction execution must agree."""
+    from see_ml_b200.engine import Context, MODE_CONTRACT, MODE_FUSED
+    from see_ml_b200.formats import Op
+    T, Kx, N, r = 512, 256, 256, 16
+    rng = np.random.default_rng(21)
+    sizes = dict(g=T * N, B=r * N, t=T * r, X=T * Kx, A=Kx * r, p=T * Kx, ds=T * N, dB=r * N, dx1=T * Kx, a1=T * Kx,
+                 dx2=T * Kx, dt_out=T * Kx)
+    off, cur = {}, 0
+    for name, n in sizes.items():
+        off[name] = cur
+        cur = F.align_up(cur + 4 * n, 256)
+    off["dt"] = off["dt_out"]          # the result's slot starts where dt lives
+    off["out"] = off["dt_out"]
+    off["dA"] = off["p"]               # dA takes the addend's slot
+    W = opcases._rn(rng, Kx, N)
+    arena = np.zeros(cur + 256, np.uint8)
+    vals = dict(g=opcases._rn(rng, T, N), B=opcases._rn(rng, r, N), t=opcases._rn(rng, T, r), X=opcases._rn(rng, T, Kx),
+                A=opcases._rn(rng, Kx, r), p=opcases._rn(rng, T, Kx))
+    for name, v in vals.items():
+        arena[off[name]:off[name] + v.nbytes] = v.view(np.uint8).reshape(-1)
+    w = F.RODATA_BIT | 0
+    I = opcases._ins
+    sc = F.f32_bits(2.0)
+    prog = np.concatenate([
+        I(Op.SCALE, [off["g"], off["ds"], sc], [T * N]), I(Op.GEMM_NT, [off["ds"], off["B"], off["dt"]], [T, r, N]),
+        I(Op.GEMM_TN, [off["t"], off["ds"], off["dB"]], [r, N, T]), I(Op.GEMM_NT, [off["dt"], off["A"], off["dx1"]], [T, Kx, r]),
+        I(Op.ADD, [off["p"], off["dx1"], off["a1"]], [T * Kx]), I(Op.GEMM_TN, [off["X"], off["dt"], off["dA"]], [Kx, r, T]),
+        I(Op.GEMM_NT, [off["g"], w, off["dx2"]], [T, Kx, N]), I(Op.ADD, [off["a1"], off["dx2"], off["out"]], [T * Kx])])
+    res = {}
+    for mode in (MODE_CONTRACT, MODE_FUSED):
+        for gemm in (0, 1):
+            ctx = Context(arena.size, W.view(np.uint8).reshape(-1), gemm=gemm)
+            ctx.write(0, arena)
+            pid = ctx.build(prog, mode=mode)
+            ctx.run(pid, 0, len(prog))
+            res[(mode, gemm)] = {k: ctx.read(off[k], 4 * n).view(np.float32).copy()
+                                 for k, n in (("out", T * Kx), ("dA", Kx * r), ("dB", r * N))}
+            res[(mode, gemm)]["launches"] = ctx.launches(pid)
+            ctx.close()
+    g64, B64, t64, X64, A64, p64, W64 = (v.astype(np.float64) for v in (vals["g"], vals["B"], vals["t"], vals["X"], vals["A"],
+                                                                           vals["p"], W))
+    dt64 = 2.0 * g64 @ B64.T
+    want = {"out": p64 + dt64 @ A64.T + g64 @ W64.T, "dA": X64.T @ dt64, "dB": t64.T @ (2.0 * g64)}
+    import tol
+    for key, got in res.items():
+        for k in ("out", "dA", "dB"):
+            tol.assert_close(got[k], want[k], f"{key} {k}")
+    assert res[(MODE_FUSED, 0)]["launches"] < res[(MODE_CONTRACT, 0)]["launches"], "the group was not fused"
