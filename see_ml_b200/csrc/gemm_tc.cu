@@ -1341,7 +1341,6 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
   auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
   auto bar_acc_full = [&](int b) { return bars + 8u * (3 * STAGES + b); };
   auto bar_acc_empty = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
-  const uint32_t bar_epi = bars + 8u * (3 * STAGES + 4);
   const uint32_t tmem_slot = bars + 8u * (3 * STAGES + 5);
   volatile uint32_t* tmem_slot_ptr =
       reinterpret_cast<volatile uint32_t*>(base_ptr + STAGES * S::kStage + S::kEpi + 8 * (3 * STAGES + 5));
@@ -1383,7 +1382,6 @@ gemm_tc_pair_f16p_kernel(const __grid_constant__ CUtensorMap mapAhi, const __gri
       mbar_init(bar_acc_full(b), 1);
       mbar_init(bar_acc_empty(b), 2 * kWorkers / 32);
     }
-    mbar_init(bar_epi, kWorkers / 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
