@@ -126,12 +126,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full(s), 1);
-      mbar_init(bar_split(s), kWorkers);
+      mbar_init(bar_split(s), kWorkers / 32);        // one arrival per worker warp
       mbar_init(bar_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full(b), 1);
-      mbar_init(bar_acc_empty(b), kWorkers);
+      mbar_init(bar_acc_empty(b), kWorkers / 32);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -249,7 +249,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         }
       }
       tc_fence_before();
-      mbar_arrive(bar_acc_empty(buf));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty(buf));
       return true;
     };
     for (int kb = 0; kb < nkb && ok; ++kb) {
@@ -275,7 +276,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         split_range(stg, S::kABytes);
         if (!(p.b_lo && kb < nkb1)) split_range(stg + kBOff, S::kBBytes);
         fence_async_smem();
-        mbar_arrive(bar_split(s));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_split(s));
       }
       // one k-block into chunk ci the previous chunk has been multiplied: collect it now, while
       // the tensor core works on the blocks already split
@@ -351,6 +353,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 // reduction at the tile's last row (A[m,k] = 0 for k > m), mode 3 starts it at the tile's
 // first row (A[m,k] = 0 for k < m). M % 128 == 0, N % BN == 0 and K % 32 == 0 are required
 // (windows of neighbouring heads touch, so the TMA cannot clip ragged edges here).
+// What bounds these small-tile kernels is the single thread that issues the products: measured on a
+// B200, a tcgen05.mma costs its issuing thread about 50 cycles whatever its width up to N = 64 (a
+// 128 x 256 x 8 tf32 product: 133, its arithmetic), a commit arrives about 160 cycles after it is
+// issued, and a second issuing thread raises the aggregate rate only 1.4 times. With 8 products and
+// 1.25 commits per 32-row k-block the handshakes and issues alone take ~0.45 us per k-block, at any
+// ring depth. Measured and without effect on the step time: a ring of raw tiles of its own ahead of
+// the re-laid ones (7 loads in flight), collecting warps that do nothing else, the reduction spread
+// over four TMEM accumulators (independent chains), 16 split warps, spinning on test_wait.
 struct BgParams {
   int nkb;                 // K / 32
   int causal;
@@ -387,17 +397,30 @@ __device__ __forceinline__ void split_plain(const uint8_t* raw, uint8_t* lo, int
 // raw: [32][W] f32, reduction index on rows. hi / lo: W rows of 128 bytes (K-major), 16-byte
 // chunk c of row n stored at chunk (c ^ (n & 7)) - the 128-byte swizzle. Lanes walk n, so the
 // reads are conflict-free and each quarter-warp's 128-bit stores cover all 32 banks.
-template <int W>
+// NW threads share the tile; all of a thread's loads are issued before its first store (these warps are
+// bound by the latency of their own instruction stream, not by shared-memory bandwidth).
+template <int W, int NW = kBgWorkers>
 __device__ __forceinline__ void split_transposed(const uint8_t* raw, uint8_t* hi, uint8_t* lo, int t) {
   const float* r = reinterpret_cast<const float*>(raw);
-#pragma unroll 2
-  for (int i = t; i < W * 8; i += kBgWorkers) {
-    const int n = i % W, k4 = i / W;
-    const float v0 = r[(4 * k4 + 0) * W + n], v1 = r[(4 * k4 + 1) * W + n];
-    const float v2 = r[(4 * k4 + 2) * W + n], v3 = r[(4 * k4 + 3) * W + n];
-    const int off = n * 128 + ((k4 ^ (n & 7)) << 4);
-    *reinterpret_cast<float4*>(hi + off) = make_float4(v0, v1, v2, v3);
-    *reinterpret_cast<float4*>(lo + off) = make_float4(lo_part(v0), lo_part(v1), lo_part(v2), lo_part(v3));
+  constexpr int kIter = (W * 8 + NW - 1) / NW;
+  float v[kIter][4];
+#pragma unroll
+  for (int u = 0; u < kIter; ++u) {
+    const int i = t + u * NW, n = i % W, k4 = i / W;
+    if (W * 8 % NW == 0 || i < W * 8) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[u][j] = r[(4 * k4 + j) * W + n];
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kIter; ++u) {
+    const int i = t + u * NW, n = i % W, k4 = i / W;
+    if (W * 8 % NW == 0 || i < W * 8) {
+      const int off = n * 128 + ((k4 ^ (n & 7)) << 4);
+      *reinterpret_cast<float4*>(hi + off) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
+      *reinterpret_cast<float4*>(lo + off) =
+          make_float4(lo_part(v[u][0]), lo_part(v[u][1]), lo_part(v[u][2]), lo_part(v[u][3]));
+    }
   }
 }
 
@@ -441,12 +464,12 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full(s), 1);
-      mbar_init(bar_split(s), kBgWorkers);
+      mbar_init(bar_split(s), kBgWorkers / 32);      // one arrival per split warp
       mbar_init(bar_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full(b), 1);
-      mbar_init(bar_acc_empty(b), 128);
+      mbar_init(bar_acc_empty(b), 4);
     }
     mbar_init(bar_epi, 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -571,7 +594,8 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         }
       }
       tc_fence_before();
-      mbar_arrive(bar_acc_empty(buf));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty(buf));
       return true;
     };
     for (int ti = 0; ti < ntile && ok; ++ti) {
@@ -591,7 +615,8 @@ bgemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       if (TB) split_transposed<BN>(base_ptr + b_raw(s), base_ptr + b_hi(s), base_ptr + b_lo(s), t);
       else split_plain(base_ptr + b_raw(s), base_ptr + b_lo(s), S::kB, t);
       fence_async_smem();
-      mbar_arrive(bar_split(s));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_split(s));
       if (i % kChunk == 1 && i > kChunk) {
         ok = collect(cg);
         ++cg;
@@ -1975,11 +2000,11 @@ attn_scores_softmax_kernel(const __grid_constant__ CUtensorMap mapQ, const __gri
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(q_split, kAfWorkers);
+    mbar_init(q_split, kAfWorkers / 32);       // one arrival per split warp
     mbar_init(accum, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full(s), 1);
-      mbar_init(k_split(s), kAfWorkers);
+      mbar_init(k_split(s), kAfWorkers / 32);
       mbar_init(k_empty(s), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -2057,7 +2082,8 @@ attn_scores_softmax_kernel(const __grid_constant__ CUtensorMap mapQ, const __gri
     if (ok) {
       split512(base_ptr);
       fence_async_smem();
-      mbar_arrive(q_split);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_split);
     }
     for (int j = 0; j < ntiles && ok; ++j) {
       const int s = j & 1, r = j >> 1;
@@ -2065,7 +2091,8 @@ attn_scores_softmax_kernel(const __grid_constant__ CUtensorMap mapQ, const __gri
       if (!ok) break;
       split512(base_ptr + kQ + s * kStage);
       fence_async_smem();
-      mbar_arrive(k_split(s));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(k_split(s));
     }
     if (MODE == 1 && ok) {
       // while the last products run: pull this tile's block of P toward L2 (one 128-byte line per request)
@@ -2707,6 +2734,7 @@ int launch_bg(seeml_b200_ctx* c, TcState& st, const TcBatched& g) {
   if (cudaGetLastError() != cudaSuccess) return -1;
   return 1;
 }
+
 }  // namespace
 
 // Batched per-head product on the tensor cores. 1 = launched, 0 = shape / context not
