@@ -512,6 +512,21 @@ void seeml_b200_ctx_destroy(seeml_b200_ctx* c) {
   cudaSetDevice(c->device);
   cudaStreamSynchronize(c->stream);
   cudaStreamSynchronize(c->copy_stream);
+  if (c->unit_times) {
+    static const char* const kinds[] = {"", "lora forward group", "lora backward group", "dgrad + add", "attention dS",
+                                        "swiglu forward", "swiglu backward", "rmsnorm backward + add", "xent group",
+                                        "adamw run"};
+    double tot = 0.0;
+    for (int k = 0; k < 320; ++k) tot += c->unit_ms[k];
+    std::fprintf(stderr, "seeml_b200 unit times (device ms, all runs of this context; total %.3f):\n", tot);
+    for (int k = 0; k < 320; ++k)
+      if (c->unit_n[k]) {
+        if (k >= 256) std::fprintf(stderr, "  %-24s", k - 256 < 10 ? kinds[k - 256] : "fused");
+        else std::fprintf(stderr, "  opcode %-17d", k);
+        std::fprintf(stderr, " n=%8llu  %10.3f ms  %5.1f %%\n", c->unit_n[k], c->unit_ms[k], tot > 0 ? 100.0 * c->unit_ms[k] / tot : 0.0);
+      }
+  }
+  for (cudaEvent_t ev : c->unit_events) cudaEventDestroy(ev);
   for (auto& p : c->programs)
     if (p) {
       for (auto& g : p->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
@@ -595,8 +610,10 @@ int seeml_b200_program_run(seeml_b200_ctx* c, int id, uint64_t begin, uint64_t e
   if (c->timing) CU(cudaEventRecord(c->t0, c->stream), "event record");
   upload_scalars(c, scalars);
   static const bool graphs_off = [] { const char* e = std::getenv("SEEML_B200_GRAPHS"); return e && std::atoi(e) == 0; }();
+  static const bool unit_times = [] { const char* e = std::getenv("SEEML_B200_UNIT_TIMES"); return e && std::atoi(e) != 0; }();
+  c->unit_times = unit_times;
   Program::RangeGraph* rg = nullptr;
-  if (c->use_graphs && !graphs_off && end - begin >= 8) rg = &p.graphs[std::make_pair(begin, end)];
+  if (c->use_graphs && !graphs_off && !unit_times && end - begin >= 8) rg = &p.graphs[std::make_pair(begin, end)];
   if (rg && rg->exec) {
     CU(cudaGraphLaunch(rg->exec, c->stream), "graph launch");
     p.last_launches = rg->launches;
@@ -617,9 +634,22 @@ int seeml_b200_program_run(seeml_b200_ctx* c, int id, uint64_t begin, uint64_t e
   x.launches = 1;
   int failed = 0;
   c->exec_unit += 2;
+  size_t nmark = 0;
+  auto mark = [&](int key) {                      // an event ahead of every unit, one behind the last
+    if (!unit_times) return;
+    if (nmark == c->unit_events.size()) {
+      cudaEvent_t ev = nullptr;
+      if (cudaEventCreate(&ev) != cudaSuccess) return;
+      c->unit_events.push_back(ev);
+      c->unit_keys.push_back(0);
+    }
+    c->unit_keys[nmark] = key;
+    cudaEventRecord(c->unit_events[nmark++], c->stream);
+  };
   for (uint64_t i = begin; i < end && !failed;) {
     ++c->exec_unit;
     const int32_t si = p.step_at.empty() ? -1 : p.step_at[i];
+    mark(si >= 0 && i + p.steps[si].count <= end ? 256 + (int)p.steps[si].kind : (int)p.instrs[i].opcode);
     if (si >= 0 && i + p.steps[si].count <= end) {
       const int fr = run_fused(x, p, p.steps[si]);
       if (fr < 0) { failed = 1; break; }
@@ -651,6 +681,18 @@ int seeml_b200_program_run(seeml_b200_ctx* c, int id, uint64_t begin, uint64_t e
     return failed;
   }
   p.last_launches = x.launches;
+  if (unit_times && nmark) {
+    mark(-1);
+    if (cudaEventSynchronize(c->unit_events[nmark - 1]) == cudaSuccess)
+      for (size_t u = 0; u + 1 < nmark; ++u) {
+        float ms = 0.0f;
+        const int key = c->unit_keys[u];
+        if (key >= 0 && key < 320 && cudaEventElapsedTime(&ms, c->unit_events[u], c->unit_events[u + 1]) == cudaSuccess) {
+          c->unit_ms[key] += ms;
+          ++c->unit_n[key];
+        }
+      }
+  }
   if (c->timing) {
     CU(cudaEventRecord(c->t1, c->stream), "event record");
     c->timed_valid = true;
