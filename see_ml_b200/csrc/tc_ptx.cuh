@@ -36,22 +36,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: false (and an error code left in *err) when the phase never completes.
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
-#ifdef SEEML_MBAR_TEST_SPIN
-  for (uint32_t i = 0; i < 4096; ++i)
-    if (mbar_test(bar, parity)) return true;
-#endif
   for (uint32_t i = 0; i < kSpinLimit; ++i)
     if (mbar_try(bar, parity)) return true;
   atomicCAS(err, 0, code);
