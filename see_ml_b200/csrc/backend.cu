@@ -168,13 +168,45 @@ int rank_n(seeml_b200_ctx* c, const float* A, const float* B, float* out, int M,
     }
   }
   if (bnk && gemm_tc_rank_n(c, A, bnk, out, M, n, K, alpha) == 1) return 1 + extra;
+  if (!k::skinny_n_ok(M, n, K)) {               // wider than the CUDA-core rank kernels take: the any-shape GEMM
+    k::GemmDesc d = dense_desc(A, B, out, (uint64_t)M, (uint64_t)n, (uint64_t)K);
+    d.sAm = K; d.sAk = 1;
+    if (b_is_nk) { d.sBk = 1; d.sBn = K; } else { d.sBk = n; d.sBn = 1; }
+    d.alpha = alpha;
+    return extra + k::gemm_simt(d, c->gemm_ws, c->stream);
+  }
   return extra + k::skinny_n(A, B, out, M, n, K, b_is_nk, alpha, c->stream);
+}
+
+// Whether the rank-r kernels (tensor-core or CUDA-core) take these shapes; rank 64 only with the
+// F16X2 arithmetic, whose fused GEMM carries a 64-wide tail.
+bool rank_n_ok(const seeml_b200_ctx* c, uint64_t M, uint64_t n, uint64_t K) {
+  if (k::skinny_n_ok((int)M, (int)n, (int)K)) return true;
+  return n == 64 && c->gemm_kind == SEEML_B200_GEMM_F16X2 && M >= 1024 && K >= 128 && K % 8 == 0;
+}
+bool rank_tn_ok(const seeml_b200_ctx* c, uint64_t T, uint64_t big, uint64_t small) {
+  if (k::skinny_tn_ok((int)T, (int)big, (int)small)) return true;
+  return small == 64 && c->gemm_kind == SEEML_B200_GEMM_F16X2 && gemm_tc_rank_tn_chunk_rows(T, big, small) != 0;
+}
+// Floats of workspace the tensor-core split-T product writes its chunk partials into (0: not that path).
+uint64_t rank_tn_partial_floats(uint64_t T, uint64_t big, uint64_t small) {
+  const uint64_t rows = gemm_tc_rank_tn_chunk_rows(T, big, small);
+  return rows ? (T / rows) * big * small : 0;
 }
 int rank_tn(seeml_b200_ctx* c, const float* W, const float* S, float* out, int T, int big, int small,
             int transposed, float alpha) {
   const uint64_t rows = gemm_tc_rank_tn_chunk_rows(T, big, small);
-  if (rows && gemm_tc_rank_tn(c, W, S, c->gemm_ws, T, big, small, rows) == 1)
+  if (rows && (uint64_t)(T / rows) * big * small <= c->gemm_ws_floats &&
+      gemm_tc_rank_tn(c, W, S, c->gemm_ws, T, big, small, rows) == 1)
     return 1 + k::skinny_tn_reduce_bs(c->gemm_ws, out, (int)(T / rows), big, small, transposed, alpha, c->stream);
+  if (!k::skinny_tn_ok(T, big, small)) {         // wider than the CUDA-core kernel takes: the any-shape GEMM
+    // out = alpha * W^T S as [big, small] (transposed) or alpha * S^T W as [small, big]
+    const int Mc = transposed ? big : small, Nc = transposed ? small : big;
+    k::GemmDesc d = dense_desc(transposed ? W : S, transposed ? S : W, out, (uint64_t)Mc, (uint64_t)Nc, (uint64_t)T);
+    d.sAm = 1; d.sAk = Mc; d.sBk = Nc; d.sBn = 1;
+    d.alpha = alpha;
+    return k::gemm_simt(d, c->gemm_ws, c->stream);
+  }
   return k::skinny_tn(W, S, out, c->gemm_ws, T, big, small, transposed, alpha, c->stream);
 }
 

@@ -2323,6 +2323,7 @@ bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, u
 
 constexpr uint64_t kRankKMax = 32768;       // longest reduction the rank-r F16X2 scratch holds
 constexpr uint64_t kF16TailRows = 65536;    // widest N the F16X2 tail scratch holds
+constexpr uint64_t kF16TailK = 64;          // widest low-rank tail (fp16 elements: one k-block of the pre-split kernel)
 struct TcState {
   int* err_dev = nullptr;
   bool attrs_set = false;
@@ -2345,7 +2346,7 @@ struct TcState {
   __half *tail_hi = nullptr, *tail_lo = nullptr;
   float* tail_inv = nullptr;                    // per-row 2^-e of the pre-split tail operand
   __half *rank_b_hi = nullptr, *rank_b_lo = nullptr;   // pre-split LoRA factor of the rank-r kernel, [64, kRankKMax]
-  float* rank_b_inv = nullptr;   // fp16 tiles of the low-rank tail's B operand, [kF16TailRows, 32] each
+  float* rank_b_inv = nullptr;   // fp16 copies of a rank-r product.s small operand
   std::map<std::tuple<const void*, uint64_t, uint64_t, uint32_t, uint32_t>, CUtensorMap> maps;
   std::set<const void*> smem_attr_done;   // kernels whose dynamic shared-memory limit was raised on this context's device
 };
@@ -2481,6 +2482,18 @@ int launch_pair(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   return 1;
 }
 
+// fp16 hi / lo tiles of the low-rank tail's B operand ([N, K2], K2 <= kF16TailK) and its scale.
+bool ensure_tail_buffers(TcState& st) {
+  if (st.tail_hi && st.tail_inv) return true;
+  if ((!st.tail_hi && cudaMalloc(&st.tail_hi, 2 * kF16TailRows * kF16TailK * sizeof(__half)) != cudaSuccess) ||
+      (!st.tail_inv && cudaMalloc(&st.tail_inv, kF16TailRows * sizeof(float)) != cudaSuccess)) {
+    cudaGetLastError();
+    return false;
+  }
+  st.tail_lo = st.tail_hi + kF16TailRows * kF16TailK;
+  return true;
+}
+
 // The CTA-pair kernel with the two-term fp16 split. Same shape rule as launch_pair; the main
 // pair's B must be a frozen operand with fp16 copies (made at build time) and the tail at most 32
 // wide, otherwise the three-product tf32 kernel takes the launch.
@@ -2488,14 +2501,11 @@ int launch_pair_f16(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   auto it = st.f16_copies.find(g.Bt);
   if (it == st.f16_copies.end() || g.K2 > 32 || g.N > kF16TailRows) return launch_pair(c, st, g);
   if (!ensure_smem_attr(st, gemm_tc_pair_f16_kernel, PairF16Smem::kTotal)) return -1;
-  if (!st.absmax_dev || !st.tail_hi) {
-    if ((!st.absmax_dev && cudaMalloc(&st.absmax_dev, 64) != cudaSuccess) ||
-        (!st.tail_hi && cudaMalloc(&st.tail_hi, 2 * kF16TailRows * 32 * sizeof(__half)) != cudaSuccess)) {
-      cudaGetLastError();
-      return -1;
-    }
-    st.tail_lo = st.tail_hi + kF16TailRows * 32;
+  if (!st.absmax_dev && cudaMalloc(&st.absmax_dev, 64) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
   }
+  if (!ensure_tail_buffers(st)) return -1;
   const CUtensorMap* ma = cached_map(st, g.A, g.M, g.K, BM);
   const CUtensorMap* mc = cached_map(st, g.C, g.M, g.N, 32);
   const CUtensorMap* ma2 = g.K2 ? cached_map(st, g.A2, g.M, g.K2, BM) : ma;
@@ -2583,21 +2593,16 @@ void split_a_rows(seeml_b200_ctx* c, TcState& st, const float* A, uint64_t M, ui
 }
 
 // F16X2 with pre-split operands (see gemm_tc_pair_f16p_kernel). Needs the A scratch sized at build
-// time; anything it cannot take goes to launch_pair_f16.
+// time; anything it cannot take goes to launch_pair_f16. The low-rank tail may be up to 64 wide
+// here (one k-block of 64 fp16 elements); the other kernels take 32, so a wider tail this launcher
+// cannot serve is reported as not eligible (0) and the caller runs the group unfused.
 int launch_pair_f16p(seeml_b200_ctx* c, TcState& st, const TcGemm& g) {
   auto it = st.f16_copies.find(g.Bt);
-  if (it == st.f16_copies.end() || g.K2 > 32 || (g.K2 % 8) != 0 || g.N > kF16TailRows || g.K % 8 != 0 ||
+  if (it == st.f16_copies.end() || g.K2 > kF16TailK || (g.K2 % 8) != 0 || g.N > kF16TailRows || g.K % 8 != 0 ||
       g.M * g.K > st.a_cap || g.M > st.a_rows_cap || !st.a_hi)
-    return launch_pair_f16(c, st, g);
+    return g.K2 > 32 ? 0 : launch_pair_f16(c, st, g);      // the other kernels take tails up to 32 wide
   if (!ensure_smem_attr(st, gemm_tc_pair_f16p_kernel, PairF16pSmem::kTotal)) return -1;
-  if (!st.tail_hi || !st.tail_inv) {
-    if ((!st.tail_hi && cudaMalloc(&st.tail_hi, 2 * kF16TailRows * 32 * sizeof(__half)) != cudaSuccess) ||
-        (!st.tail_inv && cudaMalloc(&st.tail_inv, kF16TailRows * sizeof(float)) != cudaSuccess)) {
-      cudaGetLastError();
-      return -1;
-    }
-    st.tail_lo = st.tail_hi + kF16TailRows * 32;
-  }
+  if (!ensure_tail_buffers(st)) return -1;
   const CUtensorMap* mah = cached_map_f16(st, st.a_hi, g.M, g.K, BM, true);
   const CUtensorMap* mal = cached_map_f16(st, st.a_lo, g.M, g.K, BM, true);
   const CUtensorMap* ma2h = g.K2 ? cached_map_f16(st, st.a2_hi, g.M, g.K2, BM, true) : mah;
@@ -2697,6 +2702,8 @@ int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g) {
   static const bool pairs = [] { const char* e = std::getenv("SEEML_B200_GEMM_PAIR"); return !e || std::atoi(e) != 0; }();
   const uint64_t m_tiles = (g.M + BM - 1) / BM;
   static const bool presplit = [] { const char* e = std::getenv("SEEML_B200_F16_PRESPLIT"); return !e || std::atoi(e) != 0; }();
+  if (g.K2 > 32 && !(g.N >= 192 && pairs && presplit && m_tiles % 2 == 0 && c->gemm_kind == SEEML_B200_GEMM_F16X2))
+    return 0;                                           // tails wider than 32: the pre-split pair kernel only
   if (g.N >= 192 && pairs && m_tiles % 2 == 0 && c->gemm_kind == SEEML_B200_GEMM_F16X2)
     r = presplit ? launch_pair_f16p(c, *st, g) : launch_pair_f16(c, *st, g);
   else if (g.N >= 192 && split && pairs && m_tiles % 2 == 0) r = launch_pair(c, *st, g);
@@ -2707,7 +2714,7 @@ int gemm_tc_launch(seeml_b200_ctx* c, const TcGemm& g) {
     st->usable = false;
     return 0;
   }
-  return 1;
+  return r;
 }
 
 namespace {
@@ -3025,7 +3032,7 @@ static int ensure_a_split(seeml_b200_ctx* c, TcState& st, uint64_t M, uint64_t K
   st.a_inv = st.a2_inv = nullptr;
   st.a_cap = st.a_rows_cap = 0;
   if (cudaMalloc(&st.a_hi, cap * 2) != cudaSuccess || cudaMalloc(&st.a_lo, cap * 2) != cudaSuccess ||
-      cudaMalloc(&st.a2_hi, rows * 32 * 2) != cudaSuccess || cudaMalloc(&st.a2_lo, rows * 32 * 2) != cudaSuccess ||
+      cudaMalloc(&st.a2_hi, rows * kF16TailK * 2) != cudaSuccess || cudaMalloc(&st.a2_lo, rows * kF16TailK * 2) != cudaSuccess ||
       cudaMalloc(&st.a_inv, rows * 4) != cudaSuccess || cudaMalloc(&st.a2_inv, rows * 4) != cudaSuccess) {
     cudaGetLastError();                 // not fatal: the launcher falls back to the in-kernel split
     cudaFree(st.a_hi); cudaFree(st.a_lo); cudaFree(st.a2_hi); cudaFree(st.a2_lo); cudaFree(st.a_inv); cudaFree(st.a2_inv);

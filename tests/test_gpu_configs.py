@@ -143,10 +143,23 @@ def test_lora_matmul_sweep_at_16384_rows(kn, gemm):
     """The MatMul / LoRA sweep at M = 16384 (entries ~N(0,1), r = 16): forward, dgrad and both
     weight gradients as the compiler's instruction sequences, fused and per instruction, against
     f64 products (full for the reductions over M, sampled rows for the [M x .] outputs)."""
+    _sweep_case(kn, 16, gemm)
+
+
+@pytest.mark.parametrize("kn", [(1024, 2816), (2816, 1024)], ids=lambda s: f"K{s[0]}xN{s[1]}")
+def test_lora_matmul_sweep_rank_64_at_16384_rows(kn):
+    """The sweep's widest adapters (r = 64) in the default arithmetic: the low-rank term rides the
+    fused GEMM as one 64-wide k-block, so the fused program must need fewer launches than the
+    instruction path, with the same parity bar."""
+    launches = _sweep_case(kn, 64, 1)
+    assert launches[0] < launches[1], "the rank-64 LoRA groups were not fused"
+
+
+def _sweep_case(kn, r, gemm):
     from see_ml_b200.engine import Context, MODE_CONTRACT, MODE_FUSED
     from see_ml_b200.formats import Op
     K, N = kn
-    M, r = 16384, 16
+    M = 16384
     alpha = 2.0 * r
     rng = np.random.default_rng(K * 11 + N)
     X, W = opcases._rn(rng, M, K), opcases._rn(rng, K, N)
@@ -174,17 +187,20 @@ def test_lora_matmul_sweep_at_16384_rows(kn, gemm):
     dT64 = (alpha / r) * (G64 @ B64.T)
     ref = {"y": X64[rows] @ W64 + (alpha / r) * T64[rows] @ B64, "dB": T64.T @ ((alpha / r) * G64), "dA": X64.T @ dT64,
            "dX": dT64[rows] @ A64.T + G64[rows] @ W64.T}
+    launches = []
     for mode in (MODE_FUSED, MODE_CONTRACT):
         ctx = Context(arena.size, ro, gemm=gemm)
         ctx.write(0, arena)
         pid = ctx.build(prog, mode=mode)
         ctx.run(pid, 0, len(prog))
+        launches.append(ctx.launches(pid))
         f = lambda off, n: ctx.read(off, 4 * n).view(np.float32)
-        tol.assert_close(f(y, M * N).reshape(M, N)[rows], ref["y"], f"K{K} N{N} mode {mode} y")
-        tol.assert_close(f(dX, M * K).reshape(M, K)[rows], ref["dX"], f"K{K} N{N} mode {mode} dX")
-        tol.assert_close(f(dB, r * N), ref["dB"], f"K{K} N{N} mode {mode} dB")
-        tol.assert_close(f(dA, K * r), ref["dA"], f"K{K} N{N} mode {mode} dA")
+        tol.assert_close(f(y, M * N).reshape(M, N)[rows], ref["y"], f"K{K} N{N} r{r} mode {mode} y")
+        tol.assert_close(f(dX, M * K).reshape(M, K)[rows], ref["dX"], f"K{K} N{N} r{r} mode {mode} dX")
+        tol.assert_close(f(dB, r * N), ref["dB"], f"K{K} N{N} r{r} mode {mode} dB")
+        tol.assert_close(f(dA, K * r), ref["dA"], f"K{K} N{N} r{r} mode {mode} dA")
         ctx.close()
+    return launches
 
 
 @pytest.mark.parametrize("gemm,name", [(1, "f16x2"), (3, "tf32")])
