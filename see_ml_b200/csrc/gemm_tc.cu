@@ -2851,7 +2851,8 @@ void gemm_tc_transpose(seeml_b200_ctx* c, const float* in, float* out, uint64_t 
 // Rows per reduction chunk of the rank-r TN product: a function of the shape only (fills
 // whole waves of 148 CTAs as far as the divisors of T allow), 0 when not eligible.
 uint64_t gemm_tc_rank_tn_chunk_rows(uint64_t T, uint64_t big, uint64_t small) {
-  if ((small != 16 && small != 32 && small != 64) || big % BM != 0 || big < BM || T < 4096) return 0;
+  // rank 64 has no CUDA-core kernel to fall back on, so it takes this path from 1024 rows on
+  if ((small != 16 && small != 32 && small != 64) || big % BM != 0 || big < BM || T < (small == 64 ? 1024u : 4096u)) return 0;
   uint64_t best = 0;
   double best_eff = 0.0;
   for (uint64_t rows : {2048ull, 1024ull, 512ull}) {

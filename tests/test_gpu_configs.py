@@ -146,20 +146,20 @@ def test_lora_matmul_sweep_at_16384_rows(kn, gemm):
     _sweep_case(kn, 16, gemm)
 
 
+@pytest.mark.parametrize("M", [2048, 16384])
 @pytest.mark.parametrize("kn", [(1024, 2816), (2816, 1024)], ids=lambda s: f"K{s[0]}xN{s[1]}")
-def test_lora_matmul_sweep_rank_64_at_16384_rows(kn):
-    """The sweep's widest adapters (r = 64) in the default arithmetic: the low-rank term rides the
-    fused GEMM as one 64-wide k-block, so the fused program must need fewer launches than the
-    instruction path, with the same parity bar."""
-    launches = _sweep_case(kn, 64, 1)
-    assert launches[0] < launches[1], "the rank-64 LoRA groups were not fused"
+def test_lora_matmul_sweep_rank_64(kn, M):
+    """The sweep's widest adapters (r = 64) in the default arithmetic, at its smallest M and at
+    16384 rows: the low-rank term rides the fused GEMM as one 64-wide k-block, so the fused program
+    must need fewer launches than the instruction path, with the same parity bar."""
+    launches = _sweep_case(kn, 64, 1, M)
+    assert launches[0] < launches[1], f"the rank-64 LoRA groups were not fused: {launches}"
 
 
-def _sweep_case(kn, r, gemm):
+def _sweep_case(kn, r, gemm, M=16384):
     from see_ml_b200.engine import Context, MODE_CONTRACT, MODE_FUSED
     from see_ml_b200.formats import Op
     K, N = kn
-    M = 16384
     alpha = 2.0 * r
     rng = np.random.default_rng(K * 11 + N)
     X, W = opcases._rn(rng, M, K), opcases._rn(rng, K, N)
