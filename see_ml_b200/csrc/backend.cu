@@ -545,18 +545,12 @@ void seeml_b200_ctx_destroy(seeml_b200_ctx* c) {
   cudaStreamSynchronize(c->stream);
   cudaStreamSynchronize(c->copy_stream);
   if (c->unit_times) {
-    static const char* const kinds[] = {"", "lora forward group", "lora backward group", "dgrad + add", "attention dS",
-                                        "swiglu forward", "swiglu backward", "rmsnorm backward + add", "xent group",
-                                        "adamw run"};
     double tot = 0.0;
-    for (int k = 0; k < 320; ++k) tot += c->unit_ms[k];
+    for (const auto& kv : c->unit_acc) tot += kv.second.first;
     std::fprintf(stderr, "seeml_b200 unit times (device ms, all runs of this context; total %.3f):\n", tot);
-    for (int k = 0; k < 320; ++k)
-      if (c->unit_n[k]) {
-        if (k >= 256) std::fprintf(stderr, "  %-24s", k - 256 < 10 ? kinds[k - 256] : "fused");
-        else std::fprintf(stderr, "  opcode %-17d", k);
-        std::fprintf(stderr, " n=%8llu  %10.3f ms  %5.1f %%\n", c->unit_n[k], c->unit_ms[k], tot > 0 ? 100.0 * c->unit_ms[k] / tot : 0.0);
-      }
+    for (const auto& kv : c->unit_acc)
+      std::fprintf(stderr, "  %-44s n=%8llu  %10.3f ms  %5.1f %%\n", kv.first.c_str(), kv.second.second, kv.second.first,
+                   tot > 0 ? 100.0 * kv.second.first / tot : 0.0);
   }
   for (cudaEvent_t ev : c->unit_events) cudaEventDestroy(ev);
   for (auto& p : c->programs)
@@ -667,21 +661,41 @@ int seeml_b200_program_run(seeml_b200_ctx* c, int id, uint64_t begin, uint64_t e
   int failed = 0;
   c->exec_unit += 2;
   size_t nmark = 0;
-  auto mark = [&](int key) {                      // an event ahead of every unit, one behind the last
-    if (!unit_times) return;
+  auto mark = [&](const std::string& label) {     // an event ahead of every unit, one behind the last
     if (nmark == c->unit_events.size()) {
       cudaEvent_t ev = nullptr;
       if (cudaEventCreate(&ev) != cudaSuccess) return;
       c->unit_events.push_back(ev);
-      c->unit_keys.push_back(0);
+      c->unit_keys.emplace_back();
     }
-    c->unit_keys[nmark] = key;
+    c->unit_keys[nmark] = label;
     cudaEventRecord(c->unit_events[nmark++], c->stream);
+  };
+  auto unit_label = [&](uint64_t i, int32_t si) {  // opcode or fused-group kind; GEMM-carrying units with their shape
+    static const char* const kinds[] = {"", "lora forward group", "lora backward group", "dgrad + add", "attention dS",
+                                        "swiglu forward", "swiglu backward", "rmsnorm backward + add", "xent group",
+                                        "adamw run"};
+    char buf[96];
+    const Instr& ins = p.instrs[i];
+    if (si >= 0) {
+      const int kind = (int)p.steps[si].kind;
+      const Instr& g = kind == FusedStep::kLoraBwd ? p.instrs[i + 1] : ins;
+      if (kind <= FusedStep::kDgradAdd)
+        std::snprintf(buf, sizeof buf, "%s %llux%llux%llu", kinds[kind], (unsigned long long)g.out[0],
+                      (unsigned long long)g.out[1], (unsigned long long)g.out[2]);
+      else std::snprintf(buf, sizeof buf, "%s", kind < 10 ? kinds[kind] : "fused group");
+    } else if (ins.opcode >= kGemmNN && ins.opcode <= kGemmAccNN) {
+      std::snprintf(buf, sizeof buf, "opcode %d %llux%llux%llu", (int)ins.opcode, (unsigned long long)ins.out[0],
+                    (unsigned long long)ins.out[1], (unsigned long long)ins.out[2]);
+    } else {
+      std::snprintf(buf, sizeof buf, "opcode %d", (int)ins.opcode);
+    }
+    return std::string(buf);
   };
   for (uint64_t i = begin; i < end && !failed;) {
     ++c->exec_unit;
     const int32_t si = p.step_at.empty() ? -1 : p.step_at[i];
-    mark(si >= 0 && i + p.steps[si].count <= end ? 256 + (int)p.steps[si].kind : (int)p.instrs[i].opcode);
+    if (unit_times) mark(unit_label(i, si >= 0 && i + p.steps[si].count <= end ? si : -1));
     if (si >= 0 && i + p.steps[si].count <= end) {
       const int fr = run_fused(x, p, p.steps[si]);
       if (fr < 0) { failed = 1; break; }
@@ -714,14 +728,14 @@ int seeml_b200_program_run(seeml_b200_ctx* c, int id, uint64_t begin, uint64_t e
   }
   p.last_launches = x.launches;
   if (unit_times && nmark) {
-    mark(-1);
+    mark(std::string());
     if (cudaEventSynchronize(c->unit_events[nmark - 1]) == cudaSuccess)
       for (size_t u = 0; u + 1 < nmark; ++u) {
         float ms = 0.0f;
-        const int key = c->unit_keys[u];
-        if (key >= 0 && key < 320 && cudaEventElapsedTime(&ms, c->unit_events[u], c->unit_events[u + 1]) == cudaSuccess) {
-          c->unit_ms[key] += ms;
-          ++c->unit_n[key];
+        if (cudaEventElapsedTime(&ms, c->unit_events[u], c->unit_events[u + 1]) == cudaSuccess) {
+          auto& acc = c->unit_acc[c->unit_keys[u]];
+          acc.first += ms;
+          ++acc.second;
         }
       }
   }

@@ -142,13 +142,12 @@ struct seeml_b200_ctx {
   uint64_t rodata_bytes = 0;
   uint32_t gemm_kind = SEEML_B200_GEMM_TF32X3;
   bool timing = false, timed_valid = false;
-  // SEEML_B200_UNIT_TIMES=1: device time per dispatched unit (graph replay off), keyed by opcode
-  // (0..255) or 256 + fused-group kind, printed when the context is destroyed.
+  // SEEML_B200_UNIT_TIMES=1: device time per dispatched unit (graph replay off), keyed by opcode or
+  // fused-group kind (GEMM-carrying units also by shape), printed when the context is destroyed.
   bool unit_times = false;
   std::vector<cudaEvent_t> unit_events;
-  std::vector<int> unit_keys;
-  double unit_ms[320] = {};
-  unsigned long long unit_n[320] = {};
+  std::vector<std::string> unit_keys;
+  std::map<std::string, std::pair<double, unsigned long long>> unit_acc;   // label -> device ms, count
   bool use_graphs = true;          // SEEML_B200_GRAPHS=0 turns graph replay off
   // serial number of the instruction / fused group being enqueued: consecutive units of one run
   // differ by one, separate runs by more (kernels use it to tell what may have changed in between)
